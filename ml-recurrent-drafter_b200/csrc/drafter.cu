@@ -1,0 +1,401 @@
+// Drafter beam-search kernels other than the GEMMs: operand staging for the recurrent update,
+// vocabulary-wide top-k warp + log-softmax with sparse output, cross-beam top-W and beam reorder,
+// categorical draws from sparse distributions.
+#include "rd_common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// rd_drafter_prepare
+template <typename T>
+__global__ void drafter_prepare_kernel(const T* __restrict__ embed, const int64_t* __restrict__ beams,
+                                       const int32_t* __restrict__ parent, const T* __restrict__ ctx, T* __restrict__ a,
+                                       T* __restrict__ x, int W, int Lb, int H, int k) {
+  const int r = blockIdx.x;
+  const int b = r / W;
+  const int64_t tok = beams[(int64_t)r * Lb + k];
+  const T* e = embed + tok * (int64_t)H;
+  T* arow = a + (int64_t)r * 2 * H;
+  T* xrow = x + (int64_t)r * 2 * H;
+  if (k == 0) {
+    const T* c = ctx + (int64_t)b * H;
+    for (int d = threadIdx.x; d < H; d += blockDim.x) {
+      arow[d] = e[d];
+      arow[H + d] = rd::Num<T>::from_f(0.f);
+      xrow[d] = c[d];
+    }
+  } else {
+    const T* s = x + ((int64_t)b * W + parent[r]) * 2 * H + H;
+    for (int d = threadIdx.x; d < H; d += blockDim.x) {
+      arow[d] = e[d];
+      arow[H + d] = s[d];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// rd_vocab_topk: one block per row.
+constexpr int kTopkThreads = 512;
+constexpr int kKept = RD_TOPK_MAX_KEPT;
+
+template <typename T>
+__global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
+    const T* __restrict__ logits, int64_t ld, int rows_max, const int32_t* __restrict__ rows_dev, int V, int top_k,
+    float mask_value, int subtract_max, float temperature, float* __restrict__ kept_val, int32_t* __restrict__ kept_idx,
+    int32_t* __restrict__ kept_cnt, float* __restrict__ masked_logp) {
+  const int row = blockIdx.x;
+  if (row >= rd::live_rows(rows_dev, rows_max)) return;
+  extern __shared__ float z[];  // [V]
+  __shared__ float red[kTopkThreads / 32];
+  __shared__ int hist[256];
+  __shared__ uint32_t sel_prefix;
+  __shared__ int sel_remaining;
+  __shared__ int n_gt, n_tie_total;
+  __shared__ int scan[kTopkThreads];
+  __shared__ float cv[kKept];
+  __shared__ int ci[kKept];
+  __shared__ float sv[kKept];
+  __shared__ int si[kKept];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T* src = logits + (int64_t)row * ld;
+
+  // 1. load, row max
+  float mx = -INFINITY;
+  for (int v = tid; v < V; v += kTopkThreads) {
+    float f = rd::Num<T>::to_f(src[v]);
+    z[v] = f;
+    mx = fmaxf(mx, f);
+  }
+  mx = rd::warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int w = 1; w < kTopkThreads / 32; ++w) mx = fmaxf(mx, red[w]);
+  __syncthreads();
+  if (subtract_max) {
+    for (int v = tid; v < V; v += kTopkThreads) z[v] = z[v] - mx;
+    mx = 0.f;
+  }
+  if (tid == 0) {
+    sel_prefix = 0;
+    sel_remaining = top_k < V ? top_k : V;
+  }
+  __syncthreads();
+
+  // 2. radix select of the top_k-th largest key, 8 bits per pass from the top
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    const uint32_t hi_mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+    for (int i = tid; i < 256; i += kTopkThreads) hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = sel_prefix;
+    for (int v = tid; v < V; v += kTopkThreads) {
+      uint32_t key = rd::float_key(z[v]);
+      if ((key & hi_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int rem = sel_remaining, d = 255;
+      for (; d > 0; --d) {
+        if (hist[d] >= rem) break;
+        rem -= hist[d];
+      }
+      sel_prefix = prefix | ((uint32_t)d << shift);
+      sel_remaining = rem;
+    }
+    __syncthreads();
+  }
+  const uint32_t thr_key = sel_prefix;  // key of the top_k-th largest value
+  if (tid == 0) {
+    n_gt = 0;
+    n_tie_total = 0;
+  }
+  __syncthreads();
+
+  // 3. entries strictly above the threshold (fewer than top_k of them), any order
+  for (int v = tid; v < V; v += kTopkThreads) {
+    if (rd::float_key(z[v]) > thr_key) {
+      int s = atomicAdd(&n_gt, 1);
+      if (s < kKept) {
+        cv[s] = z[v];
+        ci[s] = v;
+      }
+    }
+  }
+  // 4. ties at the threshold, in ascending index order, while capacity lasts
+  const int chunk = (V + kTopkThreads - 1) / kTopkThreads;
+  const int v0 = tid * chunk, v1 = min(V, v0 + chunk);
+  int my_ties = 0;
+  for (int v = v0; v < v1; ++v) my_ties += (rd::float_key(z[v]) == thr_key);
+  scan[tid] = my_ties;
+  __syncthreads();
+  for (int o = 1; o < kTopkThreads; o <<= 1) {
+    int add = tid >= o ? scan[tid - o] : 0;
+    __syncthreads();
+    scan[tid] += add;
+    __syncthreads();
+  }
+  const int gt = min(n_gt, kKept);
+  int pos = gt + scan[tid] - my_ties;
+  for (int v = v0; v < v1; ++v) {
+    if (rd::float_key(z[v]) == thr_key) {
+      if (pos < kKept) {
+        cv[pos] = z[v];
+        ci[pos] = v;
+      }
+      ++pos;
+    }
+  }
+  if (tid == kTopkThreads - 1) n_tie_total = scan[tid];
+  __syncthreads();
+  const int ties = n_tie_total;
+  const int cnt = min(kKept, gt + ties);
+
+  // 5. order the kept list by (value descending, id ascending)
+  if (tid < cnt) {
+    const float mv = cv[tid];
+    const int mi = ci[tid];
+    int rank = 0;
+    for (int o = 0; o < cnt; ++o) rank += (cv[o] > mv) || (cv[o] == mv && ci[o] < mi);
+    sv[rank] = mv;
+    si[rank] = mi;
+  }
+  __syncthreads();
+
+  // 6. log-softmax over the warped row: kept entries, ties that did not fit, and masked entries
+  if (warp == 0) {
+    const float inv_t = 1.0f;  // the division below keeps the reference's rounding
+    (void)inv_t;
+    const float top = sv[0] / temperature;
+    const float masked_s = mask_value / temperature;
+    const float m = fmaxf(top, masked_s);
+    float acc = 0.f;
+    for (int o = lane; o < cnt; o += 32) acc += expf(sv[o] / temperature - m);
+    acc = rd::warp_sum(acc);
+    const float thr_val = sv[cnt - 1];
+    const int dropped = gt + ties - cnt;
+    const int n_masked = V - gt - ties;
+    acc += (float)dropped * expf(thr_val / temperature - m);
+    acc += (float)n_masked * expf(masked_s - m);
+    const float lse = m + logf(acc);
+    for (int o = lane; o < kKept; o += 32) {
+      const bool live = o < cnt;
+      kept_val[(int64_t)row * kKept + o] = live ? (sv[o] / temperature - lse) : -INFINITY;
+      kept_idx[(int64_t)row * kKept + o] = live ? si[o] : -1;
+    }
+    if (lane == 0) {
+      kept_cnt[row] = cnt;
+      masked_logp[row] = masked_s - lse;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// rd_beam_select: one block per batch row.
+constexpr int kSelThreads = 1024;
+
+__global__ void __launch_bounds__(kSelThreads) beam_select_kernel(
+    int W, int Lb, int k, int V, const float* __restrict__ kept_val, const int32_t* __restrict__ kept_idx,
+    const int32_t* __restrict__ kept_cnt, const float* __restrict__ score_in, float* __restrict__ score_out,
+    const int64_t* __restrict__ beams_in, int64_t* __restrict__ beams_out, const int32_t* __restrict__ anc_in,
+    int32_t* __restrict__ anc_out, int32_t* __restrict__ parent_out) {
+  const int b = blockIdx.x;
+  extern __shared__ unsigned char raw[];
+  float* cs = reinterpret_cast<float*>(raw);                 // [W*W] candidate scores
+  int* cf = reinterpret_cast<int*>(cs + W * W);              // [W*W] flat index w*V+token (-1 = absent)
+  const int ncand = W * W;
+  for (int c = threadIdx.x; c < ncand; c += kSelThreads) {
+    const int w = c / W, i = c % W;
+    const int r = b * W + w;
+    const int cnt = kept_cnt[r];
+    if (i < cnt && i < kKept) {
+      const float base = (k == 0) ? (w == 0 ? 0.f : RD_LOG_0) : score_in[r];
+      cs[c] = kept_val[(int64_t)r * kKept + i] + base;
+      cf[c] = w * V + kept_idx[(int64_t)r * kKept + i];
+    } else {
+      cs[c] = -INFINITY;
+      cf[c] = -1;
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < ncand; c += kSelThreads) {
+    const int f = cf[c];
+    if (f < 0) continue;
+    const float s = cs[c];
+    int rank = 0;
+    for (int o = 0; o < ncand && rank < W; ++o) {
+      const float so = cs[o];
+      rank += (so > s) || (so == s && cf[o] >= 0 && cf[o] < f);
+    }
+    if (rank < W) {
+      const int w = c / W;
+      const int dst = b * W + rank;
+      score_out[dst] = s;
+      parent_out[dst] = w;
+      const int64_t* src_beam = beams_in + ((int64_t)b * W + w) * Lb;
+      int64_t* dst_beam = beams_out + (int64_t)dst * Lb;
+      for (int j = 0; j <= k; ++j) dst_beam[j] = src_beam[j];
+      dst_beam[k + 1] = (int64_t)(f - w * V);
+      const int32_t* src_anc = anc_in + ((int64_t)b * W + w) * (Lb - 1);
+      int32_t* dst_anc = anc_out + (int64_t)dst * (Lb - 1);
+      for (int j = 0; j < k; ++j) dst_anc[j] = src_anc[j];
+      dst_anc[k] = w;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// rd_drafter_dense_log_probs
+struct SparseLists {
+  const float* val[RD_MAX_BEAM_LENGTH];
+  const int32_t* idx[RD_MAX_BEAM_LENGTH];
+  const int32_t* cnt[RD_MAX_BEAM_LENGTH];
+  const float* masked[RD_MAX_BEAM_LENGTH];
+};
+
+__global__ void dense_log_probs_kernel(int W, int Lb, int V, SparseLists s, const int32_t* __restrict__ anc,
+                                       float* __restrict__ out) {
+  // block = (b*W + w)*(Lb-1) + j
+  const int j = blockIdx.x % (Lb - 1);
+  const int bw = blockIdx.x / (Lb - 1);
+  const int b = bw / W;
+  const int r = b * W + anc[(int64_t)bw * (Lb - 1) + j];
+  float* dst = out + (int64_t)blockIdx.x * V;
+  const float m = s.masked[j][r];
+  for (int v = threadIdx.x; v < V; v += blockDim.x) dst[v] = m;
+  __syncthreads();
+  const int cnt = s.cnt[j][r];
+  for (int o = threadIdx.x; o < cnt; o += blockDim.x) dst[s.idx[j][(int64_t)r * kKept + o]] = s.val[j][(int64_t)r * kKept + o];
+}
+
+// ---------------------------------------------------------------------------------------------
+// rd_sample_from_sparse: one warp per row.
+__global__ void sample_sparse_kernel(const float* __restrict__ kept_val, const int32_t* __restrict__ kept_idx,
+                                     const int32_t* __restrict__ kept_cnt, int rows, const float* __restrict__ uniforms,
+                                     int64_t* __restrict__ out) {
+  const int row = blockIdx.x;
+  __shared__ float p[kKept];
+  __shared__ int id[kKept];
+  const int cnt = kept_cnt[row];
+  const int t = threadIdx.x;
+  if (t < cnt) {
+    const int mi = kept_idx[(int64_t)row * kKept + t];
+    int rank = 0;
+    for (int o = 0; o < cnt; ++o) rank += kept_idx[(int64_t)row * kKept + o] < mi;
+    p[rank] = expf(kept_val[(int64_t)row * kKept + t]);
+    id[rank] = mi;
+  }
+  __syncthreads();
+  if (t == 0) {
+    float total = 0.f;
+    for (int o = 0; o < cnt; ++o) total += p[o];
+    const float target = uniforms[row] * total;
+    float c = 0.f;
+    int pick = -1, last = -1;
+    for (int o = 0; o < cnt; ++o) {
+      if (p[o] > 0.f) {
+        c += p[o];
+        last = o;
+        if (pick < 0 && c > target) pick = o;
+      }
+    }
+    if (pick < 0) pick = last >= 0 ? last : 0;
+    out[row] = id[pick];
+  }
+}
+
+}  // namespace
+
+extern "C" int rd_drafter_prepare(int dtype, const void* embed, const int64_t* beams, const int32_t* parent,
+                                  const void* ctx, void* a, void* x, int B, int W, int Lb, int H, int k, void* stream) {
+  RD_REQUIRE(embed && beams && ctx && a && x, RD_ERR_ARG);
+  RD_REQUIRE(k == 0 || parent, RD_ERR_ARG);
+  RD_REQUIRE(B >= 1 && W >= 1 && W <= RD_MAX_BEAM_WIDTH && Lb >= 2 && Lb <= RD_MAX_BEAM_LENGTH && H >= 1 && k >= 0 &&
+                 k < Lb - 1,
+             RD_ERR_SIZE);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == RD_F32)
+    drafter_prepare_kernel<float><<<B * W, 256, 0, s>>>((const float*)embed, beams, parent, (const float*)ctx,
+                                                         (float*)a, (float*)x, W, Lb, H, k);
+  else if (dtype == RD_BF16)
+    drafter_prepare_kernel<__nv_bfloat16><<<B * W, 256, 0, s>>>((const __nv_bfloat16*)embed, beams, parent,
+                                                                 (const __nv_bfloat16*)ctx, (__nv_bfloat16*)a,
+                                                                 (__nv_bfloat16*)x, W, Lb, H, k);
+  else
+    return RD_ERR_DTYPE;
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_vocab_topk(int logits_dtype, const void* logits, int64_t ld, int rows_max, const int32_t* rows_dev,
+                             int V, int top_k, float mask_value, int subtract_max, float temperature, float* kept_val,
+                             int32_t* kept_idx, int32_t* kept_cnt, float* masked_logp, void* stream) {
+  RD_REQUIRE(logits && kept_val && kept_idx && kept_cnt && masked_logp, RD_ERR_ARG);
+  RD_REQUIRE(rows_max >= 1 && V >= 1 && top_k >= 1 && top_k <= RD_TOPK_MAX_KEPT && ld >= V, RD_ERR_SIZE);
+  RD_REQUIRE(temperature > 0.f, RD_ERR_ARG);
+  const size_t smem = (size_t)V * sizeof(float);
+  RD_REQUIRE(smem <= 200 * 1024, RD_ERR_SIZE);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (logits_dtype == RD_F32) {
+    auto kern = vocab_topk_kernel<float>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<rows_max, kTopkThreads, smem, s>>>((const float*)logits, ld, rows_max, rows_dev, V, top_k, mask_value,
+                                              subtract_max, temperature, kept_val, kept_idx, kept_cnt, masked_logp);
+  } else if (logits_dtype == RD_BF16) {
+    auto kern = vocab_topk_kernel<__nv_bfloat16>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<rows_max, kTopkThreads, smem, s>>>((const __nv_bfloat16*)logits, ld, rows_max, rows_dev, V, top_k,
+                                              mask_value, subtract_max, temperature, kept_val, kept_idx, kept_cnt,
+                                              masked_logp);
+  } else {
+    return RD_ERR_DTYPE;
+  }
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_beam_select(int B, int W, int Lb, int k, int V, const float* kept_val, const int32_t* kept_idx,
+                              const int32_t* kept_cnt, const float* score_in, float* score_out,
+                              const int64_t* beams_in, int64_t* beams_out, const int32_t* anc_in, int32_t* anc_out,
+                              int32_t* parent_out, void* stream) {
+  RD_REQUIRE(kept_val && kept_idx && kept_cnt && score_out && beams_in && beams_out && anc_in && anc_out && parent_out,
+             RD_ERR_ARG);
+  RD_REQUIRE(k == 0 || score_in, RD_ERR_ARG);
+  RD_REQUIRE(B >= 1 && W >= 1 && W <= RD_MAX_BEAM_WIDTH && Lb >= 2 && Lb <= RD_MAX_BEAM_LENGTH && k >= 0 && k < Lb - 1,
+             RD_ERR_SIZE);
+  RD_REQUIRE((int64_t)W * V < (int64_t)INT32_MAX, RD_ERR_SIZE);
+  const size_t smem = (size_t)W * W * (sizeof(float) + sizeof(int));
+  beam_select_kernel<<<B, kSelThreads, smem, (cudaStream_t)stream>>>(W, Lb, k, V, kept_val, kept_idx, kept_cnt, score_in,
+                                                                    score_out, beams_in, beams_out, anc_in, anc_out,
+                                                                    parent_out);
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_drafter_dense_log_probs(int B, int W, int Lb, int V, const float* const* kept_val_host,
+                                          const int32_t* const* kept_idx_host, const int32_t* const* kept_cnt_host,
+                                          const float* const* masked_logp_host, const int32_t* anc, float* out,
+                                          void* stream) {
+  RD_REQUIRE(kept_val_host && kept_idx_host && kept_cnt_host && masked_logp_host && anc && out, RD_ERR_ARG);
+  RD_REQUIRE(B >= 1 && W >= 1 && Lb >= 2 && Lb <= RD_MAX_BEAM_LENGTH && V >= 1, RD_ERR_SIZE);
+  SparseLists s{};
+  for (int j = 0; j < Lb - 1; ++j) {
+    s.val[j] = kept_val_host[j];
+    s.idx[j] = kept_idx_host[j];
+    s.cnt[j] = kept_cnt_host[j];
+    s.masked[j] = masked_logp_host[j];
+    RD_REQUIRE(s.val[j] && s.idx[j] && s.cnt[j] && s.masked[j], RD_ERR_ARG);
+  }
+  dense_log_probs_kernel<<<B * W * (Lb - 1), 256, 0, (cudaStream_t)stream>>>(W, Lb, V, s, anc, out);
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_sample_from_sparse(const float* kept_val, const int32_t* kept_idx, const int32_t* kept_cnt, int rows,
+                                     const float* uniforms, int64_t* out, void* stream) {
+  RD_REQUIRE(kept_val && kept_idx && kept_cnt && uniforms && out, RD_ERR_ARG);
+  RD_REQUIRE(rows >= 1, RD_ERR_SIZE);
+  sample_sparse_kernel<<<rows, kKept, 0, (cudaStream_t)stream>>>(kept_val, kept_idx, kept_cnt, rows, uniforms, out);
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}

@@ -1,0 +1,499 @@
+// C = epilogue(A * W^T), bf16 operands, fp32 accumulation on the 5th-generation tensor cores.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of a 128 x 64 A tile and a BN x 64 W tile
+//              per pipeline stage (128-byte swizzle, no multicast), completion on an mbarrier;
+//   warp 1     MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16, kind::f16)
+//              from shared-memory descriptors into one of two TMEM accumulator buffers and frees
+//              stages with tcgen05.commit;
+//   warps 2-5  epilogue: tcgen05.ld of the accumulator (each warp its own 32 TMEM lanes), fused
+//              bias / SiLU / residual / SwiGLU, 16-byte global stores, overlapped with the next
+//              tile's main loop through the second accumulator buffer.
+// Tiles are walked N-major so that the CTAs running at the same time share W tiles through L2;
+// the number of live rows M may come from device memory.
+//
+// Every mbarrier wait is bounded: when a wait gives up the kernel records a code in *status,
+// stops issuing work, lets outstanding bulk copies land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "rd_common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 22;  // polls, each followed by a short sleep
+
+struct GemmPlan {
+  CUtensorMap map_a;
+  CUtensorMap map_w;
+  int m_max, N, K, bn;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or when another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 64) {
+      if (*abort_flag) return false;
+      __nanosleep(64);
+    }
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                      // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                      // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                      // 128-byte swizzle
+  return d;
+}
+
+__device__ __forceinline__ uint32_t umma_instr_desc(int n) {
+  // fp32 accumulator, bf16 A and B, both K-major, M = 128
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct EpiArgs {
+  void* C;
+  int64_t ldc;
+  const __nv_bfloat16* bias;
+  const void* R;
+  int64_t ldr;
+};
+
+// 32 consecutive accumulator columns [n, n+32) of one row -> global memory.
+template <int EPI, bool OUT_F32>
+__device__ __forceinline__ void epilogue_store(const uint32_t* acc_bits, const EpiArgs& e, int64_t m, int n, int N) {
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc_bits[i]);
+  if (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (n + i < N) v[i] += __bfloat162float(e.bias[n + i]);
+  }
+  if (EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = rd::silu_f(v[i]);
+  }
+  if (EPI == RD_EPI_SWIGLU) {
+    // columns (2i, 2i+1) = (gate_i, up_i) -> output column (n/2 + i)
+    float o[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] = rd::silu_f(v[2 * i]) * v[2 * i + 1];
+    const int no = n >> 1, No = N >> 1;
+    if (OUT_F32) {
+      float* dst = (float*)e.C + m * e.ldc + no;
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (no + i < No) dst[i] = o[i];
+    } else {
+      __nv_bfloat16* dst = (__nv_bfloat16*)e.C + m * e.ldc + no;
+      if (no + 16 <= No) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint4 pk;
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(o[c * 8 + 2 * i], o[c * 8 + 2 * i + 1]);
+          reinterpret_cast<uint4*>(dst)[c] = pk;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (no + i < No) dst[i] = __float2bfloat16_rn(o[i]);
+      }
+    }
+    return;
+  }
+  const bool full = n + 32 <= N;
+  if (OUT_F32) {
+    float* dst = (float*)e.C + m * e.ldc + n;
+    if (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES) {
+      const float* r = (const float*)e.R + m * e.ldr + n;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n + i < N) v[i] += r[i];
+    }
+    if (full) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) reinterpret_cast<float4*>(dst)[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n + i < N) dst[i] = v[i];
+    }
+  } else {
+    __nv_bfloat16* dst = (__nv_bfloat16*)e.C + m * e.ldc + n;
+    if (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES) {
+      const __nv_bfloat16* r = (const __nv_bfloat16*)e.R + m * e.ldr + n;
+      if (full) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 pk = reinterpret_cast<const uint4*>(r)[c];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(h[i]);
+            v[c * 8 + 2 * i] += f.x;
+            v[c * 8 + 2 * i + 1] += f.y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (n + i < N) v[i] += __bfloat162float(r[i]);
+      }
+    }
+    if (full) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 pk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[c * 8 + 2 * i], v[c * 8 + 2 * i + 1]);
+        reinterpret_cast<uint4*>(dst)[c] = pk;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n + i < N) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+  }
+}
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageB = BN * BK * 2;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kBytes = kStages * (kStageA + kStageB) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, int EPI, bool OUT_F32>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, EpiArgs epi,
+                   int m_max, const int32_t* __restrict__ m_dev, int N, int K, int32_t* status) {
+  using L = SmemLayout<BN>;
+  constexpr int kStages = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + kStages * L::kStageA;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (L::kStageA + L::kStageB));
+  uint64_t* full = bars;                    // [kStages]
+  uint64_t* empty = bars + kStages;         // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;  // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int M = rd::live_rows(m_dev, m_max);
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_blocks = K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(2 * BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int n_tile = tile / m_tiles, m_tile = tile % m_tiles;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], L::kStageA + L::kStageB);
+          tma_load_2d(sA + stage * L::kStageA, &map_a, &full[stage], kb * BK, m_tile * BM);
+          tma_load_2d(sB + stage * L::kStageB, &map_w, &full[stage], kb * BK, n_tile * BN);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        if (atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 1);
+        // let bulk copies that are still in flight land before the CTA's shared memory goes away
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_instr_desc(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t da = umma_smem_desc(smem_u32(sA + stage * L::kStageA));
+          const uint64_t db = umma_smem_desc(smem_u32(sB + stage * L::kStageB));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advance the start address by 16 elements = 32 bytes = 2 sixteen-byte units
+            umma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+      if (!ok && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 2);
+    }
+  } else {
+    // ---------------- epilogue warps ----------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    bool ok = true;
+    int local = 0;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+      const int n_tile = tile / m_tiles, m_tile = tile % m_tiles;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int64_t m = (int64_t)m_tile * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        const int n = n_tile * BN + c * 32;
+        if (m < M && n < N) epilogue_store<EPI, OUT_F32>(r, epi, m, n, N);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+    if (!ok && lane == 0 && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 3);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+bool make_map(CUtensorMap* map, const void* base, int64_t ld_elems, int rows, int cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_elems * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int pick_bn(int N) { return N >= 2048 ? 256 : 128; }
+
+template <int BN, int EPI>
+int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t* m_dev, int32_t* status, cudaStream_t s) {
+  using L = SmemLayout<BN>;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const int tiles = ((p->m_max + BM - 1) / BM) * ((p->N + BN - 1) / BN);
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  if (out_dtype == RD_F32) {
+    auto kern = gemm_tc_kernel<BN, EPI, true>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    kern<<<grid, kThreads, L::kBytes, s>>>(p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K, status);
+  } else {
+    auto kern = gemm_tc_kernel<BN, EPI, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    kern<<<grid, kThreads, L::kBytes, s>>>(p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K, status);
+  }
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+template <int BN>
+int launch_epi(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t* m_dev, int epilogue, int32_t* status,
+               cudaStream_t s) {
+  switch (epilogue) {
+    case RD_EPI_NONE: return launch_out<BN, RD_EPI_NONE>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_BIAS: return launch_out<BN, RD_EPI_BIAS>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_BIAS_SILU: return launch_out<BN, RD_EPI_BIAS_SILU>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_BIAS_SILU_RES: return launch_out<BN, RD_EPI_BIAS_SILU_RES>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_RES: return launch_out<BN, RD_EPI_RES>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_SWIGLU: return launch_out<BN, RD_EPI_SWIGLU>(p, out_dtype, e, m_dev, status, s);
+    default: return RD_ERR_ARG;
+  }
+}
+
+}  // namespace
+
+extern "C" void* rd_gemm_plan_create(const void* A, int64_t lda, int m_max, const void* W, int64_t ldw, int N, int K) {
+  if (!A || !W || m_max < 1 || N < 1 || K < BK || K % BK != 0 || lda < K || ldw < K) return nullptr;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || (lda * 2) % 16 || (ldw * 2) % 16) return nullptr;
+  GemmPlan* p = new GemmPlan();
+  p->m_max = m_max;
+  p->N = N;
+  p->K = K;
+  p->bn = pick_bn(N);
+  if (!make_map(&p->map_a, A, lda, m_max, K, BM) || !make_map(&p->map_w, W, ldw, N, K, p->bn)) {
+    delete p;
+    return nullptr;
+  }
+  return p;
+}
+
+extern "C" void rd_gemm_plan_destroy(void* plan) { delete static_cast<GemmPlan*>(plan); }
+
+extern "C" int rd_gemm_bf16_tc(const void* plan, int out_dtype, void* C, int64_t ldc, const void* bias, const void* R,
+                               int64_t ldr, const int32_t* m_dev, int epilogue, int32_t* status, void* stream) {
+  RD_REQUIRE(plan && C, RD_ERR_ARG);
+  RD_REQUIRE(out_dtype == RD_F32 || out_dtype == RD_BF16, RD_ERR_DTYPE);
+  const GemmPlan* p = static_cast<const GemmPlan*>(plan);
+  const bool need_bias = epilogue == RD_EPI_BIAS || epilogue == RD_EPI_BIAS_SILU || epilogue == RD_EPI_BIAS_SILU_RES;
+  const bool need_res = epilogue == RD_EPI_BIAS_SILU_RES || epilogue == RD_EPI_RES;
+  RD_REQUIRE(!need_bias || bias, RD_ERR_ARG);
+  RD_REQUIRE(!need_res || R, RD_ERR_ARG);
+  RD_REQUIRE(epilogue != RD_EPI_SWIGLU || p->N % 2 == 0, RD_ERR_SIZE);
+  const int esz = out_dtype == RD_F32 ? 4 : 2;
+  RD_REQUIRE(((uintptr_t)C & 15) == 0 && (ldc * esz) % 16 == 0, RD_ERR_ALIGN);
+  RD_REQUIRE(!need_res || (((uintptr_t)R & 15) == 0 && (ldr * esz) % 16 == 0), RD_ERR_ALIGN);
+  EpiArgs e{C, ldc, (const __nv_bfloat16*)bias, R, ldr};
+  cudaStream_t s = (cudaStream_t)stream;
+  if (p->bn == 256) return launch_epi<256>(p, out_dtype, e, m_dev, epilogue, status, s);
+  return launch_epi<128>(p, out_dtype, e, m_dev, epilogue, status, s);
+}

@@ -1,0 +1,269 @@
+// Element-wise and reduction kernels of the Llama verify forward: embedding gather, RMSNorm,
+// rotary embedding + KV-cache append, row argmax, and the small data-movement helpers of the
+// decode loop.
+#include "rd_common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int64_t* __restrict__ ids, T* __restrict__ out,
+                                    int m_max, const int32_t* __restrict__ m_dev, int H) {
+  const int t = blockIdx.x;
+  if (t >= rd::live_rows(m_dev, m_max)) return;
+  const T* src = table + ids[t] * (int64_t)H;
+  T* dst = out + (int64_t)t * H;
+  for (int d = threadIdx.x; d < H; d += blockDim.x) dst[d] = src[d];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                                      int m_max, const int32_t* __restrict__ m_dev, int H, float eps) {
+  const int t = blockIdx.x;
+  if (t >= rd::live_rows(m_dev, m_max)) return;
+  const T* xr = x + (int64_t)t * H;
+  T* yr = y + (int64_t)t * H;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < H; d += 256) {
+    float v = rd::Num<T>::to_f(xr[d]);
+    ss += v * v;
+  }
+  __shared__ float red[8];
+  ss = rd::warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rs = 1.0f / sqrtf(tot / (float)H + eps);
+  for (int d = threadIdx.x; d < H; d += 256) {
+    // normalise in fp32, round to the model dtype, then scale by the weight (as the reference does)
+    T n = rd::Num<T>::from_f(rd::Num<T>::to_f(xr[d]) * rs);
+    yr[d] = rd::Num<T>::from_f(rd::Num<T>::to_f(w[d]) * rd::Num<T>::to_f(n));
+  }
+}
+
+template <typename T>
+__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache,
+                                     T* __restrict__ v_cache, const int32_t* __restrict__ tok_row,
+                                     const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_slot,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_pos, int m_max,
+                                     const int32_t* __restrict__ m_dev, int nh, int nkv, int hd, int max_len) {
+  const int t = blockIdx.x;
+  if (t >= rd::live_rows(m_dev, m_max)) return;
+  const int b = tok_row[t], slot = tok_slot[t];
+  int pos = tok_pos[t];
+  pos = pos < 0 ? 0 : (pos >= n_pos ? n_pos - 1 : pos);
+  const int half = hd / 2;
+  const int width = (nh + 2 * nkv) * hd;
+  const T* src = qkv + (int64_t)t * width;
+  const float* c = cos_t + (int64_t)pos * hd;
+  const float* s = sin_t + (int64_t)pos * hd;
+  for (int e = threadIdx.x; e < width; e += blockDim.x) {
+    const int head = e / hd, d = e % hd;
+    const float v = rd::Num<T>::to_f(src[e]);
+    if (head < nh + nkv) {
+      const float other = rd::Num<T>::to_f(d < half ? src[e + half] : src[e - half]);
+      const float rot = d < half ? -other : other;
+      // two rounded products and one rounded sum, as in q*cos + rotate_half(q)*sin
+      const float r = __fadd_rn(__fmul_rn(v, c[d]), __fmul_rn(rot, s[d]));
+      if (head < nh)
+        q_out[(int64_t)t * nh * hd + e] = rd::Num<T>::from_f(r);
+      else
+        k_cache[(((int64_t)b * nkv + (head - nh)) * max_len + slot) * hd + d] = rd::Num<T>::from_f(r);
+    } else {
+      v_cache[(((int64_t)b * nkv + (head - nh - nkv)) * max_len + slot) * hd + d] = src[e];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, int64_t ld, int m_max,
+                                                          const int32_t* __restrict__ m_dev, int V,
+                                                          int32_t* __restrict__ out32, int64_t* __restrict__ out64) {
+  const int t = blockIdx.x;
+  if (t >= rd::live_rows(m_dev, m_max)) return;
+  const float* row = logits + (int64_t)t * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int v = threadIdx.x; v < V; v += 256) {
+    const float f = row[v];
+    if (f > best || (f == best && v < bi)) {
+      best = f;
+      bi = v;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) {
+      best = ob;
+      bi = oi;
+    }
+  }
+  __shared__ float sb[8];
+  __shared__ int si[8];
+  if ((threadIdx.x & 31) == 0) {
+    sb[threadIdx.x >> 5] = best;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i)
+      if (sb[i] > best || (sb[i] == best && si[i] < bi)) {
+        best = sb[i];
+        bi = si[i];
+      }
+    if (bi == 0x7fffffff) bi = 0;
+    if (out32) out32[t] = bi;
+    if (out64) out64[t] = bi;
+  }
+}
+
+__global__ void emit_tokens_kernel(const int64_t* __restrict__ token_buf, int max_len, const int32_t* __restrict__ kv_begin,
+                                   const int32_t* __restrict__ kv_len, const int64_t* __restrict__ next_tokens,
+                                   int64_t pad_id, int out_len, int64_t* __restrict__ out) {
+  const int b = blockIdx.x;
+  const int len = kv_len[b], begin = kv_begin[b];
+  const int lead = out_len - 1 - len;  // pad ids on the left
+  for (int c = threadIdx.x; c < out_len; c += blockDim.x) {
+    int64_t v;
+    if (c == out_len - 1)
+      v = next_tokens[b];
+    else if (c < lead)
+      v = pad_id;
+    else
+      v = token_buf[(int64_t)b * max_len + begin + (c - lead)];
+    out[(int64_t)b * out_len + c] = v;
+  }
+}
+
+__global__ void commit_reference_slots_kernel(int W, int Lb, const int32_t* __restrict__ unpacker,
+                                              const int32_t* __restrict__ n_accepted,
+                                              const int32_t* __restrict__ seq_in_beam, int S, int S2,
+                                              int64_t* __restrict__ out) {
+  const int b = blockIdx.x, j = threadIdx.x;
+  if (j >= Lb) return;
+  const int A = n_accepted[b], seq = seq_in_beam[b];
+  int64_t* o = out + ((int64_t)b * Lb + j) * 3;
+  if (j <= A) {
+    o[0] = S + unpacker[((int64_t)b * W + seq) * Lb + j];
+    o[1] = S + seq * Lb + j;
+    o[2] = S2 - (A + 1) + j;
+  } else {
+    o[0] = o[1] = o[2] = -1;
+  }
+}
+
+// Cache.unpack of the reference layout: gather into scratch, then write back.
+template <typename T>
+__global__ void cache_unpack_gather_kernel(const T* __restrict__ cache, int B, int nkv, int max_len, int hd, int S,
+                                           const int64_t* __restrict__ unpacker, int n_flat, T* __restrict__ scratch) {
+  // grid (n_flat, B*nkv, NL*2)
+  const int f = blockIdx.x, bh = blockIdx.y, lk = blockIdx.z;
+  const int b = bh / nkv;
+  const int64_t src_slot = S + unpacker[(int64_t)b * n_flat + f];
+  const T* src = cache + (((int64_t)lk * B * nkv + bh) * max_len + src_slot) * hd;
+  T* dst = scratch + (((int64_t)lk * B * nkv + bh) * n_flat + f) * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = src[d];
+}
+template <typename T>
+__global__ void cache_unpack_scatter_kernel(T* __restrict__ cache, int B, int nkv, int max_len, int hd, int S, int n_flat,
+                                            const T* __restrict__ scratch) {
+  const int f = blockIdx.x, bh = blockIdx.y, lk = blockIdx.z;
+  const T* src = scratch + (((int64_t)lk * B * nkv + bh) * n_flat + f) * hd;
+  T* dst = cache + (((int64_t)lk * B * nkv + bh) * max_len + S + f) * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = src[d];
+}
+
+}  // namespace
+
+#define RD_DISPATCH_T(dtype, ...)                  \
+  if ((dtype) == RD_F32) {                         \
+    using T = float;                               \
+    __VA_ARGS__;                                   \
+  } else if ((dtype) == RD_BF16) {                 \
+    using T = __nv_bfloat16;                       \
+    __VA_ARGS__;                                   \
+  } else {                                         \
+    return RD_ERR_DTYPE;                           \
+  }
+
+extern "C" int rd_embed_gather(int dtype, const void* table, const int64_t* ids, void* out, int m_max,
+                               const int32_t* m_dev, int H, void* stream) {
+  RD_REQUIRE(table && ids && out, RD_ERR_ARG);
+  RD_REQUIRE(m_max >= 1 && H >= 1, RD_ERR_SIZE);
+  cudaStream_t s = (cudaStream_t)stream;
+  RD_DISPATCH_T(dtype, (embed_gather_kernel<T><<<m_max, 256, 0, s>>>((const T*)table, ids, (T*)out, m_max, m_dev, H)));
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_rmsnorm(int dtype, const void* x, const void* weight, void* y, int m_max, const int32_t* m_dev, int H,
+                          float eps, void* stream) {
+  RD_REQUIRE(x && weight && y, RD_ERR_ARG);
+  RD_REQUIRE(m_max >= 1 && H >= 1, RD_ERR_SIZE);
+  cudaStream_t s = (cudaStream_t)stream;
+  RD_DISPATCH_T(dtype,
+                (rmsnorm_kernel<T><<<m_max, 256, 0, s>>>((const T*)x, (const T*)weight, (T*)y, m_max, m_dev, H, eps)));
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_rope_kv_write(int dtype, const void* qkv, void* q_out, void* k_cache, void* v_cache,
+                                const int32_t* tok_row, const int32_t* tok_pos, const int32_t* tok_slot,
+                                const float* cos_table, const float* sin_table, int n_pos, int m_max,
+                                const int32_t* m_dev, int nh, int nkv, int hd, int max_len, void* stream) {
+  RD_REQUIRE(qkv && q_out && k_cache && v_cache && tok_row && tok_pos && tok_slot && cos_table && sin_table, RD_ERR_ARG);
+  RD_REQUIRE(m_max >= 1 && nh >= 1 && nkv >= 1 && hd >= 2 && hd % 2 == 0 && max_len >= 1 && n_pos >= 1, RD_ERR_SIZE);
+  cudaStream_t s = (cudaStream_t)stream;
+  RD_DISPATCH_T(dtype, (rope_kv_write_kernel<T><<<m_max, 256, 0, s>>>((const T*)qkv, (T*)q_out, (T*)k_cache, (T*)v_cache,
+                                                                      tok_row, tok_pos, tok_slot, cos_table, sin_table,
+                                                                      n_pos, m_max, m_dev, nh, nkv, hd, max_len)));
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_argmax_rows(const float* logits, int64_t ld, int m_max, const int32_t* m_dev, int V, int32_t* out32,
+                              int64_t* out64, void* stream) {
+  RD_REQUIRE(logits && (out32 || out64), RD_ERR_ARG);
+  RD_REQUIRE(m_max >= 1 && V >= 1 && ld >= V, RD_ERR_SIZE);
+  argmax_rows_kernel<<<m_max, 256, 0, (cudaStream_t)stream>>>(logits, ld, m_max, m_dev, V, out32, out64);
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_emit_tokens(const int64_t* token_buf, int max_len, const int32_t* kv_begin, const int32_t* kv_len,
+                              const int64_t* next_tokens, int64_t pad_id, int B, int out_len, int64_t* out,
+                              void* stream) {
+  RD_REQUIRE(token_buf && kv_begin && kv_len && next_tokens && out, RD_ERR_ARG);
+  RD_REQUIRE(B >= 1 && out_len >= 1 && max_len >= 1, RD_ERR_SIZE);
+  emit_tokens_kernel<<<B, 256, 0, (cudaStream_t)stream>>>(token_buf, max_len, kv_begin, kv_len, next_tokens, pad_id,
+                                                         out_len, out);
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_commit_reference_slots(int B, int W, int Lb, const int32_t* unpacker, const int32_t* n_accepted,
+                                         const int32_t* seq_in_beam, int S, int S2, int64_t* out, void* stream) {
+  RD_REQUIRE(unpacker && n_accepted && seq_in_beam && out, RD_ERR_ARG);
+  RD_REQUIRE(B >= 1 && W >= 1 && Lb >= 1 && Lb <= RD_MAX_BEAM_LENGTH, RD_ERR_SIZE);
+  commit_reference_slots_kernel<<<B, 32, 0, (cudaStream_t)stream>>>(W, Lb, unpacker, n_accepted, seq_in_beam, S, S2, out);
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+extern "C" int rd_cache_unpack(int dtype, void* cache, int NL, int B, int nkv, int max_len, int hd, int S,
+                               const int64_t* unpacker, int n_flat, void* scratch, void* stream) {
+  RD_REQUIRE(cache && unpacker && scratch, RD_ERR_ARG);
+  RD_REQUIRE(NL >= 1 && B >= 1 && nkv >= 1 && hd >= 1 && S >= 0 && n_flat >= 1 && S + n_flat <= max_len &&
+                 (int64_t)B * nkv <= 65535 && NL * 2 <= 65535,
+             RD_ERR_SIZE);
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(n_flat, B * nkv, NL * 2);
+  RD_DISPATCH_T(dtype, {
+    cache_unpack_gather_kernel<T><<<grid, 64, 0, s>>>((const T*)cache, B, nkv, max_len, hd, S, unpacker, n_flat, (T*)scratch);
+    cache_unpack_scatter_kernel<T><<<grid, 64, 0, s>>>((T*)cache, B, nkv, max_len, hd, S, n_flat, (const T*)scratch);
+  });
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}

@@ -1,0 +1,251 @@
+"""The ReDrafter decode loop on the B200 kernels, with the reference's interface
+(recurrent_drafting/recurrent_drafting.py): RecurrentDrafting(llm, drafter).generate(ledger,
+input_ids, max_length, beam_shape, sampling_args, special_tokens) yields the (batch, <= max_length)
+int64 token matrix after every step.
+
+One step enqueues, without reading anything back:
+  drafter beam search -> prefix-tree pack (flat rows, cache slots, RoPE positions, bitmask)
+  -> Llama verify forward over the packed tokens (K/V written straight into the cache)
+  -> LM head -> argmax (greedy) or sparse top-50 log-softmax (sampling)
+  -> acceptance + commit of the accepted path's tokens, K/V rows and next-step inputs.
+Then one small device->host copy (row lengths, accepted counts) sizes the yielded tensor.
+
+Cache rows never move: row b keeps the left offset the prompt's padding gave it
+(kv_begin[b]) and only grows (kv_len[b]).  The reference re-right-aligns every row after each step;
+its slot numbering is available in index space through reference_commit_slots().
+"""
+from dataclasses import dataclass
+from typing import Generator, Optional, Tuple
+
+import torch
+
+from . import _lib, kv_cache, modeling_drafter, modeling_llama, stats, tree_attention
+
+
+@dataclass
+class SamplingArgs:
+    temperature: float
+    greedy: bool
+
+
+@dataclass
+class SpecialTokens:
+    pad: int
+    eos: Optional[int] = 1
+
+
+def _count_left_paddings(tokens: torch.Tensor, pad_token_id: int) -> torch.Tensor:
+    """Number of leading pad ids of every row (recurrent_drafting.py:387-388)."""
+    return torch.sum(torch.cumprod(torch.eq(tokens, pad_token_id).to(torch.int64), dim=-1), dim=-1)
+
+
+def _greedy_choose_from_candidates(beams_by_drafter: torch.Tensor, beams_by_llm: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(n_tokens_in_seq, seq_in_beam) for per-beam (unpacked) LLM tokens (recurrent_drafting.py:468-496).
+    Runs the acceptance kernel with an identity unpacker and no cache."""
+    B, W, Lb = beams_by_drafter.shape
+    dev = beams_by_drafter.device
+    beams = beams_by_drafter.to(torch.int64).contiguous()
+    llm_tok = beams_by_llm.to(torch.int32).reshape(-1).contiguous()
+    unpacker = torch.arange(W * Lb, dtype=torch.int32, device=dev).repeat(B).contiguous()
+    row_start = torch.arange(B + 1, dtype=torch.int32, device=dev) * (W * Lb)
+    n = torch.empty(B, dtype=torch.int32, device=dev)
+    seq = torch.empty(B, dtype=torch.int32, device=dev)
+    nxt = torch.empty(B, dtype=torch.int64, device=dev)
+    _lib.call("rd_accept_commit_greedy", _lib.F32, _lib.ptr(beams), B, W, Lb, _lib.ptr(unpacker), _lib.ptr(row_start),
+              _lib.ptr(llm_tok), None, 0, None, 0, 0, 0, 0, None, None, None, None, _lib.ptr(n), _lib.ptr(seq), _lib.ptr(nxt),
+              None, _lib.stream())
+    return n.long(), seq.long()
+
+
+class _DecodeState:
+    """Device buffers of one generate() call."""
+
+    def __init__(self, llm, B: int, W: int, Lb: int, max_len: int, device):
+        H = llm.config.hidden_size
+        i32 = dict(dtype=torch.int32, device=device)
+        self.kv_begin = torch.zeros(B, **i32)
+        self.small = torch.zeros(2, B, **i32)  # row 0: kv_len, row 1: n_accepted (one read-back per step)
+        self.kv_len = self.small[0]
+        self.n_accepted = self.small[1]
+        self.small_host = torch.zeros(2, B, dtype=torch.int32).pin_memory()
+        self.seq_in_beam = torch.zeros(B, **i32)
+        self.token_buf = torch.zeros(B, max_len, dtype=torch.int64, device=device)
+        self.ctx = torch.zeros(B, H, dtype=llm.dtype, device=device)
+        self.init_tok = torch.zeros(B, dtype=torch.int64, device=device)
+        self.llm_tok = torch.zeros(B * W * Lb, **i32)
+        self.fp = tree_attention.alloc_flat(B, W, Lb, device)
+        self.p = modeling_drafter.new_sparse(B * W * Lb, device)
+        self.status = torch.zeros(1, **i32)
+
+
+class RecurrentDrafting(torch.nn.Module):
+    def __init__(self, llm: modeling_llama.LlamaForCausalLM, drafter: modeling_drafter.Drafter):
+        super().__init__()
+        self.llm = llm
+        self.drafter = drafter
+        self.last_state: Optional[_DecodeState] = None
+
+    def llm_n_kv_heads(self) -> int:
+        if isinstance(self.llm, modeling_llama.LlamaForCausalLM):
+            return self.llm.n_kv_heads
+        raise TypeError(f"Unsupported base model type {type(self.llm)}")
+
+    def generate(self, ledger: stats.Ledger, input_ids: torch.Tensor, max_length: int,
+                 beam_shape: modeling_drafter.BeamShape = modeling_drafter.BeamShape(10, -1),
+                 sampling_args: SamplingArgs = SamplingArgs(1.0, False),
+                 special_tokens: SpecialTokens = SpecialTokens(0, 1)) -> Generator[torch.Tensor, None, None]:
+        with torch.inference_mode():
+            with stats.text_generation(ledger) as r:
+                for output_tokens in self._generate(r, input_ids, max_length, beam_shape, sampling_args, special_tokens):
+                    yield output_tokens
+
+    # ------------------------------------------------------------------------------------------
+    def _comprehend_prompt(self, st: _DecodeState, cache: kv_cache.Cache, input_ids: torch.Tensor,
+                           sampling_args: SamplingArgs, pad_token_id: int) -> int:
+        """Prefill (recurrent_drafting.py:391-434) over the non-pad tokens only.  Fills the cache,
+        st.ctx (hidden state of every row's last token) and st.init_tok.  Returns max row length."""
+        llm = self.llm
+        B, Lp = input_ids.shape
+        dev = input_ids.device
+        pads = _count_left_paddings(input_ids, pad_token_id)
+        n_new = Lp - pads
+        assert int(n_new.min().item()) >= 1, "a prompt row holds only padding"
+        cols = torch.arange(Lp, device=dev)[None, :].expand(B, Lp)
+        live = cols >= pads[:, None]
+        tok_ids = input_ids[live].contiguous()
+        M = tok_ids.numel()
+        tok_row = torch.arange(B, device=dev)[:, None].expand(B, Lp)[live].to(torch.int32)
+        tok_slot = cols[live].to(torch.int32)
+        tok_pos = (cols - pads[:, None])[live].to(torch.int32)
+        row_start = torch.zeros(B + 1, dtype=torch.int32, device=dev)
+        row_start[1:] = torch.cumsum(n_new, 0).to(torch.int32)
+        st.kv_begin.copy_(pads.to(torch.int32))
+        base_len = torch.zeros(B, dtype=torch.int32, device=dev)
+        ws = llm.workspace(M, B)
+        hidden = llm.backbone(ws, cache._cache, M, None, tok_ids, tok_row, tok_pos, tok_slot, row_start, st.kv_begin,
+                              base_len, B, Lp, Lp, _lib.ATTN_CAUSAL, n_pos=cache._cache.shape[4] + 1)
+        last = (row_start[1:] - 1).long()
+        st.ctx.copy_(hidden[last])
+        logits = llm.lm_logits(st.ctx, ws["logits"])
+        V = logits.shape[1]
+        if sampling_args.greedy:
+            _lib.call("rd_argmax_rows", _lib.ptr(logits), logits.stride(0), B, None, V, None, _lib.ptr(st.init_tok), _lib.stream())
+        else:
+            sp = modeling_drafter.vocab_topk(logits, modeling_drafter.new_sparse(B, dev), subtract_max=False,
+                                             temperature=sampling_args.temperature)
+            u = torch.rand(B, device=dev)
+            _lib.call("rd_sample_from_sparse", _lib.ptr(sp.val), _lib.ptr(sp.idx), _lib.ptr(sp.cnt), B, _lib.ptr(u),
+                      _lib.ptr(st.init_tok), _lib.stream())
+        st.kv_len.copy_(n_new.to(torch.int32))
+        st.token_buf[:, :Lp] = input_ids
+        for k, v in cache.sliced:
+            k.length = v.length = Lp
+        return int(n_new.max().item())
+
+    def _step(self, st: _DecodeState, cache: kv_cache.Cache, beam_shape, sampling_args: SamplingArgs, s_max: int,
+              rec: stats.TextGeneration.Step) -> None:
+        """Enqueues one decode step (recurrent_drafting.py:626-679).  No host synchronisation."""
+        llm, drafter = self.llm, self.drafter
+        B = st.kv_begin.shape[0]
+        W, Lb = beam_shape.width, beam_shape.length
+        code = _lib.dtype_code(llm.dtype)
+        sm = _lib.stream()
+        cache_t = cache._cache
+        NL, _, _, nkv, max_len, hd = cache_t.shape
+        H = llm.config.hidden_size
+        with rec.time("generate_candidates"):
+            draft = drafter.beam_search_sparse(st.ctx, st.init_tok, llm.get_input_embeddings(), beam_shape)
+        with rec.time("verify_candidates"):
+            fp = tree_attention.pack_flat(draft.beams, st.kv_begin, st.kv_len, out=st.fp)
+            m_max = B * W * Lb
+            ws = llm.workspace(m_max, m_max)
+            with rec.time("base_forward"):
+                hidden = llm.backbone(ws, cache_t, m_max, fp.m_dev, fp.tokens, fp.tok_row, fp.tok_pos, fp.tok_slot,
+                                      fp.row_start, st.kv_begin, fp.base_len, B, W * Lb, s_max + W * Lb, _lib.ATTN_TREE,
+                                      tree_mask=fp.tree_mask, mask_words=fp.mask_words, n_pos=max_len + 1)
+                logits = llm.lm_logits(hidden, ws["logits"], m_dev=fp.m_dev)
+        V = logits.shape[1]
+        with rec.time("accept_candidate_tokens"):
+            if sampling_args.greedy:
+                _lib.call("rd_argmax_rows", _lib.ptr(logits), logits.stride(0), m_max, _lib.ptr(fp.m_dev), V,
+                          _lib.ptr(st.llm_tok), None, sm)
+                _lib.call("rd_accept_commit_greedy", code, _lib.ptr(draft.beams), B, W, Lb, _lib.ptr(fp.unpacker),
+                          _lib.ptr(fp.row_start), _lib.ptr(st.llm_tok), _lib.ptr(hidden), H, _lib.ptr(cache_t), NL, nkv,
+                          max_len, hd, _lib.ptr(st.kv_begin), _lib.ptr(fp.base_len), _lib.ptr(st.kv_len),
+                          _lib.ptr(st.token_buf), _lib.ptr(st.n_accepted), _lib.ptr(st.seq_in_beam), _lib.ptr(st.init_tok),
+                          _lib.ptr(st.ctx), sm)
+            else:
+                modeling_drafter.vocab_topk(logits, st.p, subtract_max=False, temperature=sampling_args.temperature,
+                                            rows_dev=fp.m_dev)
+                u = torch.rand(B, W, Lb - 1, device=logits.device)
+                u_next = torch.rand(B, device=logits.device)
+                q = draft.q
+                _lib.call("rd_accept_commit_sample", code, _lib.ptr(draft.beams), B, W, Lb, V, _lib.ptr(fp.unpacker),
+                          _lib.ptr(fp.row_start), _lib.ptr(st.p.val), _lib.ptr(st.p.idx), _lib.ptr(st.p.cnt),
+                          _lib.ptr(st.p.masked), _lib.ptr_array([x.val for x in q]), _lib.ptr_array([x.idx for x in q]),
+                          _lib.ptr_array([x.cnt for x in q]), _lib.ptr_array([x.masked for x in q]), _lib.ptr(draft.anc),
+                          _lib.ptr(u), _lib.ptr(u_next), _lib.ptr(hidden), H, _lib.ptr(cache_t), NL, nkv, max_len, hd,
+                          _lib.ptr(st.kv_begin), _lib.ptr(fp.base_len), _lib.ptr(st.kv_len), _lib.ptr(st.token_buf),
+                          _lib.ptr(st.n_accepted), _lib.ptr(st.seq_in_beam), _lib.ptr(st.init_tok), _lib.ptr(st.ctx),
+                          None, sm)
+
+    def _generate(self, text_generation: stats.TextGeneration, input_ids: torch.Tensor, max_length: int,
+                  beam_shape: modeling_drafter.BeamShape, sampling_args: SamplingArgs,
+                  special_tokens: SpecialTokens) -> Generator[torch.Tensor, None, None]:
+        assert input_ids.dtype == torch.long, f"input_ids.dtype {input_ids.dtype} is not long"
+        if not input_ids.is_cuda:
+            raise _lib.RedrafterError("input_ids must live on a CUDA device: this package has no CPU path")
+        llm = self.llm
+        B, seq_len = input_ids.shape
+        init_seq_len = seq_len
+        W, Lb = beam_shape.width, beam_shape.length
+        dev = input_ids.device
+        cache = kv_cache.Cache(
+            batch_size=B,
+            max_length=max_length + Lb * W,
+            n_layers=llm.n_layers,
+            n_heads=self.llm_n_kv_heads(),
+            head_dim=llm.head_dim,
+            dtype=llm.dtype,
+            device=dev,
+        )
+        st = _DecodeState(llm, B, W, Lb, max_length + Lb * W, dev)
+        llm.gemm_status = st.status
+        self.last_state = st
+        s_max = self._comprehend_prompt(st, cache, input_ids, sampling_args, special_tokens.pad)
+        ref_len = seq_len  # the reference's padded sequence length S before the step
+        while seq_len < max_length:
+            with text_generation.step() as rec:
+                self._step(st, cache, beam_shape, sampling_args, s_max, rec)
+                st.small_host.copy_(st.small, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                s_max = int(st.small_host[0].max())
+                out = torch.empty(B, s_max + 1, dtype=torch.int64, device=dev)
+                _lib.call("rd_emit_tokens", _lib.ptr(st.token_buf), st.token_buf.shape[1], _lib.ptr(st.kv_begin),
+                          _lib.ptr(st.kv_len), _lib.ptr(st.init_tok), int(special_tokens.pad), B, s_max + 1, _lib.ptr(out),
+                          _lib.stream())
+                self.last_ref_lengths = (ref_len, s_max)
+                ref_len = s_max
+                for k, v in cache.sliced:
+                    k.length = v.length = s_max
+                seq_len = out.shape[1]
+                rec.set({"input_id_length": seq_len, "avg_num_accepted": int(st.small_host[1].sum()) / B})
+                yield out[:, :max_length] if seq_len > max_length else out
+                if special_tokens.eos is not None and bool(
+                    ((out[:, init_seq_len:] == special_tokens.eos).sum(dim=-1) > 0).sum() == B
+                ):
+                    break
+        if int(st.status.item()) != 0:
+            raise _lib.RedrafterError(f"a tensor-core GEMM gave up waiting on its pipeline (status {int(st.status.item())})")
+
+    def reference_commit_slots(self, beam_shape: modeling_drafter.BeamShape) -> torch.Tensor:
+        """[B, Lb, 3] int64: the last step's commit in the reference's right-aligned slot numbering
+        (source slot after the verify forward, after Cache.unpack, and final slot)."""
+        st = self.last_state
+        B = st.kv_begin.shape[0]
+        W, Lb = beam_shape.width, beam_shape.length
+        S, S2 = self.last_ref_lengths
+        out = torch.empty(B, Lb, 3, dtype=torch.int64, device=st.kv_begin.device)
+        _lib.call("rd_commit_reference_slots", B, W, Lb, _lib.ptr(st.fp.unpacker), _lib.ptr(st.n_accepted),
+                  _lib.ptr(st.seq_in_beam), S, S2, _lib.ptr(out), _lib.stream())
+        return out

@@ -1,0 +1,88 @@
+"""Drafter kernels: vocabulary top-k/log-softmax, cross-beam selection, whole beam search."""
+import numpy as np
+import pytest
+import torch
+
+import model_builders as mb
+from gpu_helpers import bf16_round, build_models, t
+from oracle import drafter as odr
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,subtract,temp", [(1000, True, 1.0), (32000, True, 1.0), (32000, False, 0.7), (320, False, 1.3), (40, True, 1.0)])
+def test_vocab_topk_vs_oracle(dtype, V, subtract, temp):
+    import recurrent_drafting as rd
+
+    md = rd.modeling_drafter
+    rs = np.random.RandomState(V)
+    rows = 9
+    logits = (rs.standard_normal((rows, V)) * 3).astype(np.float32)
+    logits[2, 5] = logits[2, 17] = logits[2].max() + 1.0  # tie at the top
+    tl = t(logits).to(dtype)
+    logits = tl.float().cpu().numpy()
+    sp = md.vocab_topk(tl, md.new_sparse(rows, "cuda"), subtract_max=subtract, temperature=temp)
+    z = odr.maintain_logits(logits) if subtract else logits
+    want = odr.log_softmax(odr.warp_logits(z) / np.float32(temp))
+    val, idx, cnt, masked = (x.cpu().numpy() for x in (sp.val, sp.idx, sp.cnt, sp.masked))
+    for r in range(rows):
+        kept = np.nonzero(odr.warp_logits(z)[r] > -49000)[0]
+        n = min(len(kept), 64)
+        assert cnt[r] == n
+        order = sorted(kept, key=lambda v: (-want[r, v], v))[:n]
+        assert list(idx[r, :n]) == order
+        np.testing.assert_allclose(val[r, :n], want[r, order], rtol=1e-5, atol=2e-5)
+        others = np.setdiff1d(np.arange(V), kept)
+        if len(others):
+            np.testing.assert_allclose(masked[r], want[r, others[0]], rtol=1e-6)
+    assert idx[2, 0] == 5 and idx[2, 1] == 17
+
+
+def test_beam_search_fp32_vs_reference_fixture(g_model):
+    """Beams equal to the reference's, log-probs within fp32 noise (fixture from the reference)."""
+    import recurrent_drafting as rd
+
+    llm, dr, lw, dw = build_models(mb.NANO_LLAMA, mb.NANO_DRAFTER, 31)
+    beams, logq = dr.beam_search_candidates(t(g_model["bs_state"]), t(g_model["bs_tok"]), llm.get_input_embeddings(),
+                                            rd.modeling_drafter.BeamShape(5, 4))
+    assert np.array_equal(beams.cpu().numpy(), g_model["bs_beams"])
+    assert logq.dtype == torch.float32 and tuple(logq.shape) == g_model["bs_logq"].shape
+    np.testing.assert_allclose(logq.cpu().numpy(), g_model["bs_logq"], rtol=1e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("B,W,Lb", [(2, 4, 3), (3, 45, 5), (1, 50, 2), (2, 16, 8)])
+def test_beam_search_fp32_vs_oracle(B, W, Lb):
+    import recurrent_drafting as rd
+
+    llm, dr, lw, dw = build_models(mb.C1_LLAMA, mb.C1_DRAFTER, 123)
+    rs = np.random.RandomState(B * 100 + W)
+    state = rs.standard_normal((B, 256)).astype(np.float32)
+    tok = rs.randint(3, 1000, size=(B,)).astype(np.int64)
+    want_beams, want_logq = odr.beam_search_candidates(dw, 1, state, tok, lw["model.embed_tokens.weight"], W, Lb)
+    beams, logq = dr.beam_search_candidates(t(state), t(tok), llm.get_input_embeddings(), rd.modeling_drafter.BeamShape(W, Lb))
+    assert np.array_equal(beams.cpu().numpy(), want_beams)
+    np.testing.assert_allclose(logq.cpu().numpy(), want_logq, rtol=1e-4, atol=3e-4)
+
+
+def test_beam_search_bf16_tolerance():
+    """bf16: beams are not pinned (near-ties reorder); the first iteration's candidate set and its
+    log-probs must agree with the fp32 oracle on the bf16-rounded weights."""
+    import recurrent_drafting as rd
+
+    llm, dr, lw, dw = build_models(mb.C1_LLAMA, mb.C1_DRAFTER, 123, dtype=torch.bfloat16)
+    lwr, dwr = bf16_round(lw), bf16_round(dw)
+    rs = np.random.RandomState(4)
+    B, W, Lb = 4, 8, 4
+    state = t(rs.standard_normal((B, 256)).astype(np.float32)).bfloat16()
+    tok = rs.randint(3, 1000, size=(B,)).astype(np.int64)
+    want_beams, want_logq = odr.beam_search_candidates(dwr, 1, state.float().cpu().numpy(), tok, lwr["model.embed_tokens.weight"], W, Lb)
+    beams, logq = dr.beam_search_candidates(state, t(tok), llm.get_input_embeddings(), rd.modeling_drafter.BeamShape(W, Lb))
+    beams, logq = beams.cpu().numpy(), logq.cpu().numpy()
+    assert np.array_equal(beams[:, :, 0], want_beams[:, :, 0])
+    for b in range(B):
+        common = set(beams[b, :, 1]) & set(want_beams[b, :, 1])
+        assert len(common) >= W - 2
+        for v in common:
+            i, j = list(beams[b, :, 1]).index(v), list(want_beams[b, :, 1]).index(v)
+            assert abs(logq[b, i, 0, v] - want_logq[b, j, 0, v]) <= 0.08

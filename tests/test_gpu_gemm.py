@@ -1,0 +1,113 @@
+"""GEMM kernels (CUDA-core fp32/bf16 path and the tcgen05 bf16 path) against a plain fp32 matmul of
+the same (rounded) operands, every epilogue, ragged sizes, device-side row counts."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+EPIS = ["none", "bias", "bias_silu", "bias_silu_res", "res", "swiglu"]
+
+
+def _ref(a, w, bias, res, epi):
+    acc = a.float() @ w.float().T
+    if epi in ("bias", "bias_silu", "bias_silu_res"):
+        acc = acc + bias.float()
+    if epi in ("bias_silu", "bias_silu_res"):
+        acc = torch.nn.functional.silu(acc)
+    if epi in ("bias_silu_res", "res"):
+        acc = acc + res.float()
+    if epi == "swiglu":
+        acc = torch.nn.functional.silu(acc[:, 0::2]) * acc[:, 1::2]
+    return acc
+
+
+def _run(dtype, out_dtype, M, N, K, epi, m_live=None, tc=False):
+    from recurrent_drafting import _lib
+    from recurrent_drafting.modeling_llama import _Linear
+
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K)
+    a = (torch.randn(M, K, generator=g, device="cuda") * 0.5).to(dtype)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.1).to(dtype)
+    bias = (torch.randn(N, generator=g, device="cuda") * 0.5).to(dtype)
+    n_out = N // 2 if epi == "swiglu" else N
+    res = (torch.randn(M, n_out, generator=g, device="cuda")).to(out_dtype)
+    c = torch.full((M, n_out), 7.0, dtype=out_dtype, device="cuda")
+    code = EPIS.index(epi)
+    m_dev = None if m_live is None else torch.tensor([m_live], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lin = _Linear(w, bias if "bias" in epi else None)
+    if tc:
+        assert lin._tc_ok(a, a.stride(0))
+    else:
+        lin._tc_ok = lambda *_: False
+    lin(a, c, code, residual=res if "res" in epi else None, m_dev=m_dev, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = _ref(a, w, bias, res, epi)
+    live = M if m_live is None else min(m_live, M)
+    got = c.float()
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    if live > 0:
+        scale = want[:live].abs().max().item() + 1e-6
+        err = (got[:live] - want[:live]).abs().max().item()
+        assert err <= tol * scale, (err, scale)
+    if live < M:
+        assert torch.all(got[live:] == 7.0), "rows beyond the live count were written"
+
+
+@pytest.mark.parametrize("epi", EPIS)
+def test_gemm_fp32_epilogues(epi):
+    _run(torch.float32, torch.float32, 70, 130, 50, epi)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 8), (64, 64, 16), (97, 250, 33), (360, 1000, 512)])
+def test_gemm_fp32_shapes(M, N, K):
+    _run(torch.float32, torch.float32, M, N, K, "none")
+    _run(torch.float32, torch.float32, M, N, K, "res", m_live=max(1, M - 3))
+
+
+def test_gemm_simt_bf16():
+    _run(torch.bfloat16, torch.bfloat16, 70, 130, 50, "bias_silu_res")
+    _run(torch.bfloat16, torch.float32, 70, 130, 50, "none")
+
+
+@pytest.mark.parametrize("epi", EPIS)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tc_epilogues(epi, out_dtype):
+    _run(torch.bfloat16, out_dtype, 300, 512, 256, epi, tc=True)
+
+
+@pytest.mark.parametrize(
+    "M,N,K,live",
+    [
+        (128, 128, 64, None),
+        (1, 128, 64, None),
+        (129, 200, 128, None),  # ragged M and N
+        (360, 4096, 4096, None),  # BN=256 path, many k-blocks, several tiles per CTA
+        (1800, 2048, 512, 921),  # device-side row count
+        (1800, 2048, 512, 0),
+        (400, 32000, 256, None),  # vocabulary-sized N
+    ],
+)
+def test_gemm_tc_shapes(M, N, K, live):
+    _run(torch.bfloat16, torch.bfloat16, M, N, K, "none", m_live=live, tc=True)
+    _run(torch.bfloat16, torch.float32, M, N, K, "res", m_live=live, tc=True)
+
+
+def test_gemm_tc_strided_output():
+    """The drafter writes the recurrent state into the right half of a [M, 2H] buffer."""
+    from recurrent_drafting import _lib
+    from recurrent_drafting.modeling_llama import _Linear
+
+    M, H = 90, 256
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = (torch.randn(M, 2 * H, generator=g, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(H, 2 * H, generator=g, device="cuda") * 0.1).bfloat16()
+    b = (torch.randn(H, generator=g, device="cuda") * 0.1).bfloat16()
+    x = torch.zeros(M, 2 * H, dtype=torch.bfloat16, device="cuda")
+    _Linear(w, b)(a, x[:, H:], _lib.EPI_BIAS_SILU)
+    torch.cuda.synchronize()
+    want = torch.nn.functional.silu(a.float() @ w.float().T + b.float())
+    assert torch.all(x[:, :H] == 0)
+    assert (x[:, H:].float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
