@@ -5,6 +5,7 @@
 // Exact-fp32 path: one warp per (query, head); scores are staged in shared memory, so the softmax
 // is the plain two-pass one.  Used for fp32 models and as the numerical cross-check of the
 // tensor-core path.
+#include "attention_tc.cuh"
 #include "rd_common.cuh"
 
 namespace {
@@ -97,11 +98,23 @@ extern "C" int rd_attention(int dtype, const void* q, const void* k_cache, const
   RD_REQUIRE(B >= 1 && B <= 65535 && nh >= 1 && nh <= 65535 && nkv >= 1 && nh % nkv == 0 && hd >= 1 && max_len >= 1 &&
                  max_new >= 1 && max_kv >= 1,
              RD_ERR_SIZE);
+  cudaStream_t s = (cudaStream_t)stream;
+  // bf16 with the common head sizes runs on the tensor cores; everything else (fp32 models, the
+  // reference's explicit dense mask) on the exact row-wise kernel
+  if (dtype == RD_BF16 && mode != RD_ATTN_DENSE && (hd == 128 || hd == 64)) {
+    if (hd == 128)
+      rd_attn::launch<128>(q, k_cache, v_cache, out, row_start, kv_begin, base_len, B, nh, nkv, max_len, max_new, mode,
+                           tree_mask, mask_words, s);
+    else
+      rd_attn::launch<64>(q, k_cache, v_cache, out, row_start, kv_begin, base_len, B, nh, nkv, max_len, max_new, mode,
+                          tree_mask, mask_words, s);
+    RD_CHECK_LAUNCH();
+    return RD_OK;
+  }
   const size_t smem = (size_t)kQPB * (max_kv + hd) * sizeof(float);
   RD_REQUIRE(smem <= 220 * 1024, RD_ERR_SIZE);
   const float scale = 1.0f / sqrtf((float)hd);
   dim3 grid((max_new + kQPB - 1) / kQPB, nh, B);
-  cudaStream_t s = (cudaStream_t)stream;
   if (dtype == RD_F32) {
     auto kern = attention_rowwise_kernel<float>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

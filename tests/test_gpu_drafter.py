@@ -66,23 +66,31 @@ def test_beam_search_fp32_vs_oracle(B, W, Lb):
 
 
 def test_beam_search_bf16_tolerance():
-    """bf16: beams are not pinned (near-ties reorder); the first iteration's candidate set and its
-    log-probs must agree with the fp32 oracle on the bf16-rounded weights."""
+    """bf16: beams are not pinned (near-ties reorder).  With beam_length 2 the beams are the top-W
+    candidates of one iteration: their set and log-probs must agree with the fp32 oracle holding
+    the same bf16-rounded weights; longer searches must still share most prefixes."""
     import recurrent_drafting as rd
 
     llm, dr, lw, dw = build_models(mb.C1_LLAMA, mb.C1_DRAFTER, 123, dtype=torch.bfloat16)
     lwr, dwr = bf16_round(lw), bf16_round(dw)
     rs = np.random.RandomState(4)
-    B, W, Lb = 4, 8, 4
+    B, W = 4, 8
     state = t(rs.standard_normal((B, 256)).astype(np.float32)).bfloat16()
-    tok = rs.randint(3, 1000, size=(B,)).astype(np.int64)
-    want_beams, want_logq = odr.beam_search_candidates(dwr, 1, state.float().cpu().numpy(), tok, lwr["model.embed_tokens.weight"], W, Lb)
-    beams, logq = dr.beam_search_candidates(state, t(tok), llm.get_input_embeddings(), rd.modeling_drafter.BeamShape(W, Lb))
+    tok_np = rs.randint(3, 1000, size=(B,)).astype(np.int64)
+    tok = t(tok_np)
+    emb = lwr["model.embed_tokens.weight"]
+    want_beams, want_logq = odr.beam_search_candidates(dwr, 1, state.float().cpu().numpy(), tok_np, emb, W, 2)
+    beams, logq = dr.beam_search_candidates(state, tok, llm.get_input_embeddings(), rd.modeling_drafter.BeamShape(W, 2))
     beams, logq = beams.cpu().numpy(), logq.cpu().numpy()
     assert np.array_equal(beams[:, :, 0], want_beams[:, :, 0])
     for b in range(B):
         common = set(beams[b, :, 1]) & set(want_beams[b, :, 1])
-        assert len(common) >= W - 2
+        assert len(common) >= W - 2, (b, beams[b, :, 1], want_beams[b, :, 1])
         for v in common:
             i, j = list(beams[b, :, 1]).index(v), list(want_beams[b, :, 1]).index(v)
             assert abs(logq[b, i, 0, v] - want_logq[b, j, 0, v]) <= 0.08
+    want4, _ = odr.beam_search_candidates(dwr, 1, state.float().cpu().numpy(), tok_np, emb, W, 4)
+    got4, _ = dr.beam_search_candidates(state, tok, llm.get_input_embeddings(), rd.modeling_drafter.BeamShape(W, 4))
+    got4 = got4.cpu().numpy()
+    same = sum(tuple(r) in {tuple(x) for x in want4[b]} for b in range(B) for r in got4[b])
+    assert same >= B * W // 2, same

@@ -20,26 +20,29 @@ def test_rmsnorm_and_argmax():
     x = rs.standard_normal((37, 200)).astype(np.float32)
     w = (1 + 0.1 * rs.standard_normal(200)).astype(np.float32)
     y = torch.empty(37, 200, device="cuda")
-    _lib.call("rd_rmsnorm", _lib.F32, _lib.ptr(t(x)), _lib.ptr(t(w)), _lib.ptr(y), 37, None, 200, 1e-6, _lib.stream())
+    tx, tw = t(x), t(w)  # keep the device buffers alive across the call
+    _lib.call("rd_rmsnorm", _lib.F32, _lib.ptr(tx), _lib.ptr(tw), _lib.ptr(y), 37, None, 200, 1e-6, _lib.stream())
     np.testing.assert_allclose(y.cpu().numpy(), ollama.rms_norm(x, w, 1e-6), rtol=1e-5, atol=1e-6)
     logits = rs.standard_normal((50, 1000)).astype(np.float32)
     logits[3, 10] = logits[3, 700] = 9.0  # tie -> first index
     o32 = torch.empty(50, dtype=torch.int32, device="cuda")
     o64 = torch.empty(50, dtype=torch.int64, device="cuda")
-    _lib.call("rd_argmax_rows", _lib.ptr(t(logits)), 1000, 50, None, 1000, _lib.ptr(o32), _lib.ptr(o64), _lib.stream())
+    tl = t(logits)
+    _lib.call("rd_argmax_rows", _lib.ptr(tl), 1000, 50, None, 1000, _lib.ptr(o32), _lib.ptr(o64), _lib.stream())
     assert np.array_equal(o32.cpu().numpy(), logits.argmax(-1)) and o32[3].item() == 10
     assert np.array_equal(o64.cpu().numpy(), logits.argmax(-1))
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mode", ["causal", "tree", "dense"])
-def test_attention_modes(dtype, mode):
+def test_attention_modes(dtype, mode, hd):
     """Ragged rows with different cache offsets and lengths, GQA, all visibility modes."""
     from recurrent_drafting import _lib
 
     rs = np.random.RandomState(7)
-    B, nh, nkv, hd, max_len = 3, 4, 2, 64, 96
-    W, L = 5, 4
+    B, nh, nkv, max_len = 3, 4, 2, 420
+    W, L = 45, 5
     beams = mb.zipf_beams(B, W, L, 100, 3)
     pt = ota.dedup_prefix(beams)
     unp = ota.get_unpacker(beams, pt)
@@ -47,7 +50,7 @@ def test_attention_modes(dtype, mode):
     tree = ota.causal_mask_of_packed_beams(unp, idx)
     n_new = ota.n_selected(beams).astype(np.int32)
     kv_begin = np.array([0, 3, 1], dtype=np.int32)
-    base = np.array([10, 4, 25], dtype=np.int32)
+    base = np.array([10, 70, 133], dtype=np.int32)
     row_start = np.concatenate([[0], np.cumsum(n_new)]).astype(np.int32)
     M = int(row_start[-1])
     q = rs.standard_normal((M, nh, hd)).astype(np.float32)
@@ -70,8 +73,9 @@ def test_attention_modes(dtype, mode):
         dense_np[:, :, 0] = 1
         dense = t(dense_np)
     code = {"causal": _lib.ATTN_CAUSAL, "tree": _lib.ATTN_TREE, "dense": _lib.ATTN_DENSE}[mode]
-    _lib.call("rd_attention", _lib.dtype_code(dtype), _lib.ptr(tq), _lib.ptr(tk), _lib.ptr(tv), _lib.ptr(out), _lib.ptr(t(row_start)),
-              _lib.ptr(t(kv_begin)), _lib.ptr(t(base)), B, nh, nkv, hd, max_len, int(n_new.max()), max_kv, code,
+    t_rs, t_begin, t_base = t(row_start), t(kv_begin), t(base)
+    _lib.call("rd_attention", _lib.dtype_code(dtype), _lib.ptr(tq), _lib.ptr(tk), _lib.ptr(tv), _lib.ptr(out), _lib.ptr(t_rs),
+              _lib.ptr(t_begin), _lib.ptr(t_base), B, nh, nkv, hd, max_len, int(n_new.max()), max_kv, code,
               _lib.ptr(fp.tree_mask) if fp else None, words, _lib.ptr(dense), dense.stride(1) if dense is not None else 0,
               dense.stride(0) if dense is not None else 0, _lib.stream())
     got = out.float().cpu().numpy().reshape(M, nh, hd)
