@@ -35,6 +35,9 @@ CONFIGS = {
                 vocab_size=1000), 1, 2, 4, 3, 32, 64, "fp32", True, 1.0),
     "c2": (dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=32, num_hidden_layers=32,
                 intermediate_size=11008, vocab_size=32000), 2, 8, 45, 5, 500, 512, "bf16", True, 1.0),
+    # c2 with 4 decoder layers: same kernel shapes as c2, a few GB on the device (profiler captures)
+    "c2-4l": (dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=32, num_hidden_layers=4,
+                   intermediate_size=11008, vocab_size=32000), 2, 8, 45, 5, 500, 512, "bf16", True, 1.0),
     "c3": (dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=32, num_hidden_layers=32,
                 intermediate_size=11008, vocab_size=32000), 2, 16, 16, 5, 256, 512, "bf16", False, 1.0),
     "c4": (dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=40, num_hidden_layers=40,
@@ -153,11 +156,6 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def decode(prompt_dev, n_steps, copy_back=False, host_sink=None):
-        """Runs n_steps decode steps; returns (generated tokens over the batch, accepted per step list)."""
-        it = model.generate(rd.stats.Ledger(), prompt_dev, max_length, shape, sargs, special)
-        return it
-
     # ---- device-resident measurement: W warm-up steps, then K timed steps
     prompt_dev = prompt_host.to(dev)
     it = model.generate(rd.stats.Ledger(), prompt_dev, max_length, shape, sargs, special)
@@ -183,6 +181,13 @@ def run_ours(args):
     ms = ev0.elapsed_time(ev1)
     tokens = st.small_host[0].sum().item() - len0
     it.close()
+
+    if args.value_only:
+        if world > 1:
+            dist.destroy_process_group()
+        return {"metric": METRIC, "value": round(tokens / (ms * 1e-3), 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": Wm,
+                "ms_per_step": round(ms / K, 4), "impl": "ours", "config": {"workload": args.config}, "gpu_launches": launches,
+                "note": "value only (profiling run)"} if rank == 0 else None
 
     # ---- roofline pass: event pairs around every tensor-core GEMM launch of a few more steps
     prof = []
@@ -368,6 +373,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--value-only", action="store_true", help="skip the roofline, end-to-end and CPU passes (profiler runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -377,7 +383,7 @@ def main():
         return
     line = run_ours(args)
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.value_only:
             line["cpu_baseline"] = run_cpu(args, False)
         print(json.dumps(line), flush=True)
 

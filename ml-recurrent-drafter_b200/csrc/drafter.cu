@@ -82,16 +82,28 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
   }
   __syncthreads();
 
-  // 2. radix select of the top_k-th largest key, 8 bits per pass from the top
-  for (int pass = 0; pass < 4; ++pass) {
+  // 2. radix select of the top_k-th largest key, 8 bits per pass from the top.  bf16 inputs have
+  //    16 significant key bits unless the row maximum was subtracted (the difference is fp32).
+  const int n_pass = (sizeof(T) == 2 && !subtract_max) ? 2 : 4;
+  for (int pass = 0; pass < n_pass; ++pass) {
     const int shift = 24 - 8 * pass;
     const uint32_t hi_mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
     for (int i = tid; i < 256; i += kTopkThreads) hist[i] = 0;
     __syncthreads();
     const uint32_t prefix = sel_prefix;
-    for (int v = tid; v < V; v += kTopkThreads) {
-      uint32_t key = rd::float_key(z[v]);
-      if ((key & hi_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+    // logits crowd into a few exponent bins: aggregate equal digits inside the warp so that one
+    // lane per distinct digit does the shared-memory atomic
+    for (int v0 = 0; v0 < V; v0 += kTopkThreads) {
+      const int v = v0 + tid;
+      uint32_t key = 0;
+      bool in = false;
+      if (v < V) {
+        key = rd::float_key(z[v]);
+        in = (key & hi_mask) == prefix;
+      }
+      const uint32_t digit = in ? ((key >> shift) & 255u) : 256u;
+      const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+      if (in && lane == (__ffs(peers) - 1)) atomicAdd(&hist[digit], __popc(peers));
     }
     __syncthreads();
     if (tid == 0) {
@@ -192,6 +204,13 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
 
 // ---------------------------------------------------------------------------------------------
 // rd_beam_select: one block per batch row.
+//
+// Every row's kept list is sorted by (log-prob descending, id ascending), so adding the row's beam
+// score keeps it non-increasing.  The candidates' total order is (score descending, beam index
+// ascending, position in the beam's list ascending) - for distinct scores that is torch.topk's
+// order, for equal scores it is the flat-index order w*V+token whenever the tie is exact in the
+// log-probs as well.  A candidate's rank is its own position plus, for every other beam, the number
+// of entries that precede it, found by binary search; ranks below W are the new beams.
 constexpr int kSelThreads = 1024;
 
 __global__ void __launch_bounds__(kSelThreads) beam_select_kernel(
@@ -201,42 +220,52 @@ __global__ void __launch_bounds__(kSelThreads) beam_select_kernel(
     int32_t* __restrict__ anc_out, int32_t* __restrict__ parent_out) {
   const int b = blockIdx.x;
   extern __shared__ unsigned char raw[];
-  float* cs = reinterpret_cast<float*>(raw);                 // [W*W] candidate scores
-  int* cf = reinterpret_cast<int*>(cs + W * W);              // [W*W] flat index w*V+token (-1 = absent)
+  float* cs = reinterpret_cast<float*>(raw);  // [W][W] candidate scores, row w = beam w's list
+  int* len = reinterpret_cast<int*>(cs + W * W);  // [W] usable length of each list
+  for (int w = threadIdx.x; w < W; w += kSelThreads) {
+    const int cnt = kept_cnt[b * W + w];
+    len[w] = min(min(cnt, W), kKept);
+  }
+  __syncthreads();
   const int ncand = W * W;
   for (int c = threadIdx.x; c < ncand; c += kSelThreads) {
     const int w = c / W, i = c % W;
     const int r = b * W + w;
-    const int cnt = kept_cnt[r];
-    if (i < cnt && i < kKept) {
-      const float base = (k == 0) ? (w == 0 ? 0.f : RD_LOG_0) : score_in[r];
-      cs[c] = kept_val[(int64_t)r * kKept + i] + base;
-      cf[c] = w * V + kept_idx[(int64_t)r * kKept + i];
-    } else {
-      cs[c] = -INFINITY;
-      cf[c] = -1;
-    }
+    const float base = (k == 0) ? (w == 0 ? 0.f : RD_LOG_0) : score_in[r];
+    cs[c] = (i < len[w]) ? kept_val[(int64_t)r * kKept + i] + base : -INFINITY;
   }
   __syncthreads();
   for (int c = threadIdx.x; c < ncand; c += kSelThreads) {
-    const int f = cf[c];
-    if (f < 0) continue;
+    const int w = c / W, i = c % W;
+    if (i >= len[w]) continue;
     const float s = cs[c];
-    int rank = 0;
-    for (int o = 0; o < ncand && rank < W; ++o) {
-      const float so = cs[o];
-      rank += (so > s) || (so == s && cf[o] >= 0 && cf[o] < f);
+    int rank = i;
+    for (int o = 0; o < W && rank < W; ++o) {
+      if (o == w) continue;
+      // entries of list o that precede (s, w): score > s, or score == s when o < w
+      const float* lo_list = cs + o * W;
+      int lo = 0, hi = len[o];
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        const float v = lo_list[mid];
+        const bool before = (o < w) ? (v >= s) : (v > s);
+        if (before)
+          lo = mid + 1;
+        else
+          hi = mid;
+      }
+      rank += lo;
     }
     if (rank < W) {
-      const int w = c / W;
       const int dst = b * W + rank;
+      const int r = b * W + w;
       score_out[dst] = s;
       parent_out[dst] = w;
-      const int64_t* src_beam = beams_in + ((int64_t)b * W + w) * Lb;
+      const int64_t* src_beam = beams_in + (int64_t)r * Lb;
       int64_t* dst_beam = beams_out + (int64_t)dst * Lb;
       for (int j = 0; j <= k; ++j) dst_beam[j] = src_beam[j];
-      dst_beam[k + 1] = (int64_t)(f - w * V);
-      const int32_t* src_anc = anc_in + ((int64_t)b * W + w) * (Lb - 1);
+      dst_beam[k + 1] = (int64_t)kept_idx[(int64_t)r * kKept + i];
+      const int32_t* src_anc = anc_in + (int64_t)r * (Lb - 1);
       int32_t* dst_anc = anc_out + (int64_t)dst * (Lb - 1);
       for (int j = 0; j < k; ++j) dst_anc[j] = src_anc[j];
       dst_anc[k] = w;
@@ -364,7 +393,7 @@ extern "C" int rd_beam_select(int B, int W, int Lb, int k, int V, const float* k
   RD_REQUIRE(B >= 1 && W >= 1 && W <= RD_MAX_BEAM_WIDTH && Lb >= 2 && Lb <= RD_MAX_BEAM_LENGTH && k >= 0 && k < Lb - 1,
              RD_ERR_SIZE);
   RD_REQUIRE((int64_t)W * V < (int64_t)INT32_MAX, RD_ERR_SIZE);
-  const size_t smem = (size_t)W * W * (sizeof(float) + sizeof(int));
+  const size_t smem = (size_t)W * W * sizeof(float) + (size_t)W * sizeof(int);
   beam_select_kernel<<<B, kSelThreads, smem, (cudaStream_t)stream>>>(W, Lb, k, V, kept_val, kept_idx, kept_cnt, score_in,
                                                                     score_out, beams_in, beams_out, anc_in, anc_out,
                                                                     parent_out);

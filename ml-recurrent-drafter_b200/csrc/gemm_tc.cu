@@ -1,16 +1,24 @@
 // C = epilogue(A * W^T), bf16 operands, fp32 accumulation on the 5th-generation tensor cores.
 //
+// The decode step has few activation rows (M = packed tree tokens, a few hundred to ~1500, known
+// only on the device) and large weights, so the WEIGHT rows ride the MMA's M dimension (128 per
+// tile) and the tokens its N dimension: N may be any multiple of 16 up to 256, chosen per tile at
+// run time, so the token rows are split into equal chunks with almost no padding (M = 900 costs
+// 912 columns instead of 1024 rows).  The accumulator tile is C^T: TMEM lane = output feature,
+// TMEM column = token, so a warp's store of one token covers 32 consecutive features.
+//
 // Persistent, warp-specialised kernel, one CTA per SM:
-//   warp 0     TMA producer: cp.async.bulk.tensor loads of a 128 x 64 A tile and a BN x 64 W tile
-//              per pipeline stage (128-byte swizzle, no multicast), completion on an mbarrier;
-//   warp 1     MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16, kind::f16)
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of a 128 x 64 W tile and one or two
+//              128 x 64 token tiles per pipeline stage (128-byte swizzle, no multicast),
+//              completion on an mbarrier;
+//   warp 1     MMA issuer: one elected thread issues tcgen05.mma (M=128, N=tokens, K=16, kind::f16)
 //              from shared-memory descriptors into one of two TMEM accumulator buffers and frees
 //              stages with tcgen05.commit;
 //   warps 2-5  epilogue: tcgen05.ld of the accumulator (each warp its own 32 TMEM lanes), fused
-//              bias / SiLU / residual / SwiGLU, 16-byte global stores, overlapped with the next
+//              bias / SiLU / residual / SwiGLU, coalesced global stores, overlapped with the next
 //              tile's main loop through the second accumulator buffer.
-// Tiles are walked N-major so that the CTAs running at the same time share W tiles through L2;
-// the number of live rows M may come from device memory.
+// Tiles are walked weight-tile-major so that the CTAs running at the same time share W tiles
+// through L2.
 //
 // Every mbarrier wait is bounded: when a wait gives up the kernel records a code in *status,
 // stops issuing work, lets outstanding bulk copies land, frees its TMEM and returns.
@@ -20,16 +28,17 @@
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int BM = 128;       // weight rows per tile (MMA M)
+constexpr int kMaxChunk = 256;  // tokens per tile (MMA N), multiple of 16
+constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr uint32_t kSpinLimit = 1u << 22;  // polls, each followed by a short sleep
 
 struct GemmPlan {
-  CUtensorMap map_a;
-  CUtensorMap map_w;
-  int m_max, N, K, bn;
+  CUtensorMap map_a;  // activations [m_max, K], box 64 x 128
+  CUtensorMap map_w;  // weights [N, K], box 64 x 128
+  int m_max, N, K;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -86,8 +95,29 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
 }
 
 __device__ __forceinline__ uint32_t umma_instr_desc(int n) {
-  // fp32 accumulator, bf16 A and B, both K-major, M = 128
+  // fp32 accumulator, bf16 A and B, both K-major, M = 128, N = n (multiple of 16, <= 256)
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// Token chunking shared by all roles: n_chunks equal chunks of `chunk` tokens (a multiple of 16).
+struct Chunking {
+  int n_chunks, chunk;
+};
+__device__ __forceinline__ Chunking make_chunking(int M) {
+  Chunking c;
+  c.n_chunks = (M + kMaxChunk - 1) / kMaxChunk;
+  if (c.n_chunks < 1) c.n_chunks = 1;
+  const int per = (M + c.n_chunks - 1) / c.n_chunks;
+  c.chunk = ((per + 15) / 16) * 16;
+  if (c.chunk < 16) c.chunk = 16;
+  return c;
+}
+// MMA N of chunk ci: its live tokens rounded up to 16
+__device__ __forceinline__ int chunk_cols(const Chunking& c, int ci, int M) {
+  int live = M - ci * c.chunk;
+  if (live > c.chunk) live = c.chunk;
+  if (live < 1) live = 1;
+  return ((live + 15) / 16) * 16;
 }
 
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
@@ -126,126 +156,62 @@ struct EpiArgs {
   int64_t ldr;
 };
 
-// 32 consecutive accumulator columns [n, n+32) of one row -> global memory.
+// 32 consecutive accumulator columns of one TMEM lane = 32 tokens [tok0, tok0+32) of output
+// feature n.  All lanes of the warp run this together (the SwiGLU pairing shuffles).
 template <int EPI, bool OUT_F32>
-__device__ __forceinline__ void epilogue_store(const uint32_t* acc_bits, const EpiArgs& e, int64_t m, int n, int N) {
-  float v[32];
+__device__ __forceinline__ void epilogue_store(const uint32_t* acc_bits, const EpiArgs& e, int n, int tok0, int M /*token limit*/, int N) {
+  const bool n_ok = n < N;
+  float bias = 0.f;
+  if (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES)
+    bias = n_ok ? __bfloat162float(e.bias[n]) : 0.f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc_bits[i]);
-  if (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (n + i < N) v[i] += __bfloat162float(e.bias[n + i]);
-  }
-  if (EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = rd::silu_f(v[i]);
-  }
-  if (EPI == RD_EPI_SWIGLU) {
-    // columns (2i, 2i+1) = (gate_i, up_i) -> output column (n/2 + i)
-    float o[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) o[i] = rd::silu_f(v[2 * i]) * v[2 * i + 1];
-    const int no = n >> 1, No = N >> 1;
-    if (OUT_F32) {
-      float* dst = (float*)e.C + m * e.ldc + no;
-#pragma unroll
-      for (int i = 0; i < 16; ++i)
-        if (no + i < No) dst[i] = o[i];
-    } else {
-      __nv_bfloat16* dst = (__nv_bfloat16*)e.C + m * e.ldc + no;
-      if (no + 16 <= No) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint4 pk;
-          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(o[c * 8 + 2 * i], o[c * 8 + 2 * i + 1]);
-          reinterpret_cast<uint4*>(dst)[c] = pk;
-        }
+  for (int i = 0; i < 32; ++i) {
+    const int tok = tok0 + i;
+    float v = __uint_as_float(acc_bits[i]) + bias;
+    if (EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) v = rd::silu_f(v);
+    if (EPI == RD_EPI_SWIGLU) {
+      // weight rows (2i, 2i+1) = (gate_i, up_i) sit in adjacent lanes
+      const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+      if ((n & 1) == 0 && tok < M && n + 1 < N) {
+        const float o = rd::silu_f(v) * up;
+        if (OUT_F32)
+          ((float*)e.C)[(int64_t)tok * e.ldc + (n >> 1)] = o;
+        else
+          ((__nv_bfloat16*)e.C)[(int64_t)tok * e.ldc + (n >> 1)] = __float2bfloat16_rn(o);
+      }
+      continue;
+    }
+    if (tok < M && n_ok) {
+      if (OUT_F32) {
+        if (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES) v += ((const float*)e.R)[(int64_t)tok * e.ldr + n];
+        ((float*)e.C)[(int64_t)tok * e.ldc + n] = v;
       } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (no + i < No) dst[i] = __float2bfloat16_rn(o[i]);
+        if (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES)
+          v += __bfloat162float(((const __nv_bfloat16*)e.R)[(int64_t)tok * e.ldr + n]);
+        ((__nv_bfloat16*)e.C)[(int64_t)tok * e.ldc + n] = __float2bfloat16_rn(v);
       }
-    }
-    return;
-  }
-  const bool full = n + 32 <= N;
-  if (OUT_F32) {
-    float* dst = (float*)e.C + m * e.ldc + n;
-    if (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES) {
-      const float* r = (const float*)e.R + m * e.ldr + n;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (n + i < N) v[i] += r[i];
-    }
-    if (full) {
-#pragma unroll
-      for (int c = 0; c < 8; ++c) reinterpret_cast<float4*>(dst)[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (n + i < N) dst[i] = v[i];
-    }
-  } else {
-    __nv_bfloat16* dst = (__nv_bfloat16*)e.C + m * e.ldc + n;
-    if (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES) {
-      const __nv_bfloat16* r = (const __nv_bfloat16*)e.R + m * e.ldr + n;
-      if (full) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint4 pk = reinterpret_cast<const uint4*>(r)[c];
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float2 f = __bfloat1622float2(h[i]);
-            v[c * 8 + 2 * i] += f.x;
-            v[c * 8 + 2 * i + 1] += f.y;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (n + i < N) v[i] += __bfloat162float(r[i]);
-      }
-    }
-    if (full) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 pk;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[c * 8 + 2 * i], v[c * 8 + 2 * i + 1]);
-        reinterpret_cast<uint4*>(dst)[c] = pk;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (n + i < N) dst[i] = __float2bfloat16_rn(v[i]);
     }
   }
 }
 
-template <int BN>
 struct SmemLayout {
-  static constexpr int kStageA = BM * BK * 2;
-  static constexpr int kStageB = BN * BK * 2;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kBytes = kStages * (kStageA + kStageB) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kStageW = BM * BK * 2;         // 16 KB
+  static constexpr int kStageA = kMaxChunk * BK * 2;  // 32 KB: two 128-token boxes back to back
+  static constexpr int kStages = 4;
+  static constexpr int kBytes = kStages * (kStageW + kStageA) + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int BN, int EPI, bool OUT_F32>
+template <int EPI, bool OUT_F32>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, EpiArgs epi,
                    int m_max, const int32_t* __restrict__ m_dev, int N, int K, int32_t* status) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout;
   constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + kStages * L::kStageA;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (L::kStageA + L::kStageB));
+  uint8_t* sW = smem;
+  uint8_t* sA = smem + kStages * L::kStageW;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (L::kStageW + L::kStageA));
   uint64_t* full = bars;                    // [kStages]
   uint64_t* empty = bars + kStages;         // [kStages]
   uint64_t* acc_full = bars + 2 * kStages;  // [2]
@@ -255,9 +221,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = rd::live_rows(m_dev, m_max);
-  const int m_tiles = (M + BM - 1) / BM;
-  const int n_tiles = (N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
+  const Chunking ch = make_chunking(M);
+  const int w_tiles = (N + BM - 1) / BM;
+  const int total_tiles = M > 0 ? w_tiles * ch.n_chunks : 0;
   const int k_blocks = K / BK;
 
   if (threadIdx.x == 0) {
@@ -274,7 +240,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(2 * BN)
+                 "r"(2 * kMaxChunk)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -292,15 +258,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const int n_tile = tile / m_tiles, m_tile = tile % m_tiles;
+        const int w_tile = tile / ch.n_chunks, ci = tile % ch.n_chunks;
+        const int cols = chunk_cols(ch, ci, M);
+        const int tok0 = ci * ch.chunk;
+        const uint32_t bytes = L::kStageW + (cols > 128 ? 2 : 1) * (128 * BK * 2);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(&full[stage], L::kStageA + L::kStageB);
-          tma_load_2d(sA + stage * L::kStageA, &map_a, &full[stage], kb * BK, m_tile * BM);
-          tma_load_2d(sB + stage * L::kStageB, &map_w, &full[stage], kb * BK, n_tile * BN);
+          mbar_expect_tx(&full[stage], bytes);
+          tma_load_2d(sW + stage * L::kStageW, &map_w, &full[stage], kb * BK, w_tile * BM);
+          tma_load_2d(sA + stage * L::kStageA, &map_a, &full[stage], kb * BK, tok0);
+          if (cols > 128) tma_load_2d(sA + stage * L::kStageA + 128 * BK * 2, &map_a, &full[stage], kb * BK, tok0 + 128);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -316,12 +286,13 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t idesc = umma_instr_desc(BN);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+        const int ci = tile % ch.n_chunks;
+        const uint32_t idesc = umma_instr_desc(chunk_cols(ch, ci, M));
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
@@ -329,19 +300,19 @@ __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * kMaxChunk;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          const uint64_t dw = umma_smem_desc(smem_u32(sW + stage * L::kStageW));
           const uint64_t da = umma_smem_desc(smem_u32(sA + stage * L::kStageA));
-          const uint64_t db = umma_smem_desc(smem_u32(sB + stage * L::kStageB));
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advance the start address by 16 elements = 32 bytes = 2 sixteen-byte units
-            umma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_f16(d_tmem, dw + 2 * k, da + 2 * k, idesc, (kb | k) != 0);
           }
           umma_commit(&empty[stage]);
           if (++stage == kStages) {
@@ -359,7 +330,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
     int local = 0;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
-      const int n_tile = tile / m_tiles, m_tile = tile % m_tiles;
+      const int w_tile = tile / ch.n_chunks, ci = tile % ch.n_chunks;
+      const int cols = chunk_cols(ch, ci, M);
+      const int tok_base = ci * ch.chunk;
+      // tokens past the chunk belong to the next chunk's tile (its columns here were not computed)
+      const int tok_limit = min(M, tok_base + ch.chunk);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
@@ -367,14 +342,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc_fence_after();
-      const int64_t m = (int64_t)m_tile * BM + quarter * 32 + lane;
-      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      const int n = w_tile * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < cols; c += 32) {
         uint32_t r[32];
-        tmem_ld32(t_row + c * 32, r);
-        const int n = n_tile * BN + c * 32;
-        if (m < M && n < N) epilogue_store<EPI, OUT_F32>(r, epi, m, n, N);
+        tmem_ld32(t_row + c, r);
+        epilogue_store<EPI, OUT_F32>(r, epi, n, tok_base + c, tok_limit, N);
       }
       tc_fence_before();
       __syncwarp();
@@ -387,7 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kMaxChunk) : "memory");
   }
 }
 
@@ -419,11 +393,9 @@ bool make_map(CUtensorMap* map, const void* base, int64_t ld_elems, int rows, in
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int pick_bn(int N) { return N >= 2048 ? 256 : 128; }
-
-template <int BN, int EPI>
+template <int EPI>
 int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t* m_dev, int32_t* status, cudaStream_t s) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout;
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
@@ -431,14 +403,14 @@ int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const int tiles = ((p->m_max + BM - 1) / BM) * ((p->N + BN - 1) / BN);
+  const int tiles = ((p->m_max + kMaxChunk - 1) / kMaxChunk) * ((p->N + BM - 1) / BM);
   const int grid = tiles < sm_count ? tiles : sm_count;
   if (out_dtype == RD_F32) {
-    auto kern = gemm_tc_kernel<BN, EPI, true>;
+    auto kern = gemm_tc_kernel<EPI, true>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
     kern<<<grid, kThreads, L::kBytes, s>>>(p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K, status);
   } else {
-    auto kern = gemm_tc_kernel<BN, EPI, false>;
+    auto kern = gemm_tc_kernel<EPI, false>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
     kern<<<grid, kThreads, L::kBytes, s>>>(p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K, status);
   }
@@ -446,16 +418,15 @@ int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t
   return RD_OK;
 }
 
-template <int BN>
 int launch_epi(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t* m_dev, int epilogue, int32_t* status,
                cudaStream_t s) {
   switch (epilogue) {
-    case RD_EPI_NONE: return launch_out<BN, RD_EPI_NONE>(p, out_dtype, e, m_dev, status, s);
-    case RD_EPI_BIAS: return launch_out<BN, RD_EPI_BIAS>(p, out_dtype, e, m_dev, status, s);
-    case RD_EPI_BIAS_SILU: return launch_out<BN, RD_EPI_BIAS_SILU>(p, out_dtype, e, m_dev, status, s);
-    case RD_EPI_BIAS_SILU_RES: return launch_out<BN, RD_EPI_BIAS_SILU_RES>(p, out_dtype, e, m_dev, status, s);
-    case RD_EPI_RES: return launch_out<BN, RD_EPI_RES>(p, out_dtype, e, m_dev, status, s);
-    case RD_EPI_SWIGLU: return launch_out<BN, RD_EPI_SWIGLU>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_NONE: return launch_out<RD_EPI_NONE>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_BIAS: return launch_out<RD_EPI_BIAS>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_BIAS_SILU: return launch_out<RD_EPI_BIAS_SILU>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_BIAS_SILU_RES: return launch_out<RD_EPI_BIAS_SILU_RES>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_RES: return launch_out<RD_EPI_RES>(p, out_dtype, e, m_dev, status, s);
+    case RD_EPI_SWIGLU: return launch_out<RD_EPI_SWIGLU>(p, out_dtype, e, m_dev, status, s);
     default: return RD_ERR_ARG;
   }
 }
@@ -469,8 +440,7 @@ extern "C" void* rd_gemm_plan_create(const void* A, int64_t lda, int m_max, cons
   p->m_max = m_max;
   p->N = N;
   p->K = K;
-  p->bn = pick_bn(N);
-  if (!make_map(&p->map_a, A, lda, m_max, K, BM) || !make_map(&p->map_w, W, ldw, N, K, p->bn)) {
+  if (!make_map(&p->map_a, A, lda, m_max, K, 128) || !make_map(&p->map_w, W, ldw, N, K, BM)) {
     delete p;
     return nullptr;
   }
@@ -489,11 +459,7 @@ extern "C" int rd_gemm_bf16_tc(const void* plan, int out_dtype, void* C, int64_t
   RD_REQUIRE(!need_bias || bias, RD_ERR_ARG);
   RD_REQUIRE(!need_res || R, RD_ERR_ARG);
   RD_REQUIRE(epilogue != RD_EPI_SWIGLU || p->N % 2 == 0, RD_ERR_SIZE);
-  const int esz = out_dtype == RD_F32 ? 4 : 2;
-  RD_REQUIRE(((uintptr_t)C & 15) == 0 && (ldc * esz) % 16 == 0, RD_ERR_ALIGN);
-  RD_REQUIRE(!need_res || (((uintptr_t)R & 15) == 0 && (ldr * esz) % 16 == 0), RD_ERR_ALIGN);
   EpiArgs e{C, ldc, (const __nv_bfloat16*)bias, R, ldr};
   cudaStream_t s = (cudaStream_t)stream;
-  if (p->bn == 256) return launch_epi<256>(p, out_dtype, e, m_dev, epilogue, status, s);
-  return launch_epi<128>(p, out_dtype, e, m_dev, epilogue, status, s);
+  return launch_epi(p, out_dtype, e, m_dev, epilogue, status, s);
 }

@@ -17,15 +17,29 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int64_t* 
 
 template <typename T>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
-                                                      int m_max, const int32_t* __restrict__ m_dev, int H, float eps) {
+                                                      int m_max, const int32_t* __restrict__ m_dev, int H, float eps,
+                                                      int vectorised) {
+  constexpr int VEC = 16 / sizeof(T);
   const int t = blockIdx.x;
   if (t >= rd::live_rows(m_dev, m_max)) return;
   const T* xr = x + (int64_t)t * H;
   T* yr = y + (int64_t)t * H;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < H; d += 256) {
-    float v = rd::Num<T>::to_f(xr[d]);
-    ss += v * v;
+  if (vectorised) {
+    for (int v = threadIdx.x; v < H / VEC; v += 256) {
+      T e[VEC];
+      *reinterpret_cast<uint4*>(e) = reinterpret_cast<const uint4*>(xr)[v];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float f = rd::Num<T>::to_f(e[i]);
+        ss += f * f;
+      }
+    }
+  } else {
+    for (int d = threadIdx.x; d < H; d += 256) {
+      float v = rd::Num<T>::to_f(xr[d]);
+      ss += v * v;
+    }
   }
   __shared__ float red[8];
   ss = rd::warp_sum(ss);
@@ -35,19 +49,36 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, c
 #pragma unroll
   for (int i = 0; i < 8; ++i) tot += red[i];
   const float rs = 1.0f / sqrtf(tot / (float)H + eps);
-  for (int d = threadIdx.x; d < H; d += 256) {
-    // normalise in fp32, round to the model dtype, then scale by the weight (as the reference does)
-    T n = rd::Num<T>::from_f(rd::Num<T>::to_f(xr[d]) * rs);
-    yr[d] = rd::Num<T>::from_f(rd::Num<T>::to_f(w[d]) * rd::Num<T>::to_f(n));
+  // normalise in fp32, round to the model dtype, then scale by the weight (as the reference does)
+  if (vectorised) {
+    for (int v = threadIdx.x; v < H / VEC; v += 256) {
+      T e[VEC], g[VEC], o[VEC];
+      *reinterpret_cast<uint4*>(e) = reinterpret_cast<const uint4*>(xr)[v];
+      *reinterpret_cast<uint4*>(g) = reinterpret_cast<const uint4*>(w)[v];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const T n = rd::Num<T>::from_f(rd::Num<T>::to_f(e[i]) * rs);
+        o[i] = rd::Num<T>::from_f(rd::Num<T>::to_f(g[i]) * rd::Num<T>::to_f(n));
+      }
+      reinterpret_cast<uint4*>(yr)[v] = *reinterpret_cast<const uint4*>(o);
+    }
+  } else {
+    for (int d = threadIdx.x; d < H; d += 256) {
+      T n = rd::Num<T>::from_f(rd::Num<T>::to_f(xr[d]) * rs);
+      yr[d] = rd::Num<T>::from_f(rd::Num<T>::to_f(w[d]) * rd::Num<T>::to_f(n));
+    }
   }
 }
 
+// One block per token.  A work item is a pair of 16-byte chunks (d .. d+VEC) and (d+hd/2 .. ) of one
+// q or k head - the two halves that the NeoX rotation mixes - or one 16-byte chunk of a v head.
 template <typename T>
-__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache,
-                                     T* __restrict__ v_cache, const int32_t* __restrict__ tok_row,
-                                     const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_slot,
-                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_pos, int m_max,
-                                     const int32_t* __restrict__ m_dev, int nh, int nkv, int hd, int max_len) {
+__global__ void __launch_bounds__(256) rope_kv_write_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    const int32_t* __restrict__ tok_row, const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_slot,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_pos, int m_max,
+    const int32_t* __restrict__ m_dev, int nh, int nkv, int hd, int max_len) {
+  constexpr int VEC = 16 / sizeof(T);
   const int t = blockIdx.x;
   if (t >= rd::live_rows(m_dev, m_max)) return;
   const int b = tok_row[t], slot = tok_slot[t];
@@ -58,20 +89,31 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, T* __restrict__ 
   const T* src = qkv + (int64_t)t * width;
   const float* c = cos_t + (int64_t)pos * hd;
   const float* s = sin_t + (int64_t)pos * hd;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) {
-    const int head = e / hd, d = e % hd;
-    const float v = rd::Num<T>::to_f(src[e]);
-    if (head < nh + nkv) {
-      const float other = rd::Num<T>::to_f(d < half ? src[e + half] : src[e - half]);
-      const float rot = d < half ? -other : other;
-      // two rounded products and one rounded sum, as in q*cos + rotate_half(q)*sin
-      const float r = __fadd_rn(__fmul_rn(v, c[d]), __fmul_rn(rot, s[d]));
-      if (head < nh)
-        q_out[(int64_t)t * nh * hd + e] = rd::Num<T>::from_f(r);
-      else
-        k_cache[(((int64_t)b * nkv + (head - nh)) * max_len + slot) * hd + d] = rd::Num<T>::from_f(r);
+  const int pairs_per_head = half / VEC;
+  const int n_rot = (nh + nkv) * pairs_per_head;
+  const int n_v = nkv * (hd / VEC);
+  for (int w = threadIdx.x; w < n_rot + n_v; w += 256) {
+    if (w < n_rot) {
+      const int head = w / pairs_per_head, d = (w % pairs_per_head) * VEC;
+      T lo[VEC], hi[VEC], olo[VEC], ohi[VEC];
+      *reinterpret_cast<uint4*>(lo) = *reinterpret_cast<const uint4*>(src + head * hd + d);
+      *reinterpret_cast<uint4*>(hi) = *reinterpret_cast<const uint4*>(src + head * hd + d + half);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float x1 = rd::Num<T>::to_f(lo[e]), x2 = rd::Num<T>::to_f(hi[e]);
+        // q*cos + rotate_half(q)*sin with two rounded products and one rounded sum
+        olo[e] = rd::Num<T>::from_f(__fadd_rn(__fmul_rn(x1, c[d + e]), __fmul_rn(-x2, s[d + e])));
+        ohi[e] = rd::Num<T>::from_f(__fadd_rn(__fmul_rn(x2, c[d + half + e]), __fmul_rn(x1, s[d + half + e])));
+      }
+      T* dst = head < nh ? q_out + (int64_t)t * nh * hd + head * hd
+                         : k_cache + (((int64_t)b * nkv + (head - nh)) * max_len + slot) * hd;
+      *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<const uint4*>(olo);
+      *reinterpret_cast<uint4*>(dst + d + half) = *reinterpret_cast<const uint4*>(ohi);
     } else {
-      v_cache[(((int64_t)b * nkv + (head - nh - nkv)) * max_len + slot) * hd + d] = src[e];
+      const int wv = w - n_rot;
+      const int head = wv / (hd / VEC), d = (wv % (hd / VEC)) * VEC;
+      const uint4 v = *reinterpret_cast<const uint4*>(src + (nh + nkv + head) * hd + d);
+      *reinterpret_cast<uint4*>(v_cache + (((int64_t)b * nkv + head) * max_len + slot) * hd + d) = v;
     }
   }
 }
@@ -203,8 +245,10 @@ extern "C" int rd_rmsnorm(int dtype, const void* x, const void* weight, void* y,
   RD_REQUIRE(x && weight && y, RD_ERR_ARG);
   RD_REQUIRE(m_max >= 1 && H >= 1, RD_ERR_SIZE);
   cudaStream_t s = (cudaStream_t)stream;
-  RD_DISPATCH_T(dtype,
-                (rmsnorm_kernel<T><<<m_max, 256, 0, s>>>((const T*)x, (const T*)weight, (T*)y, m_max, m_dev, H, eps)));
+  const int vec = dtype == RD_F32 ? 4 : 8;
+  const int vectorised = (H % vec == 0) && (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)y) % 16 == 0);
+  RD_DISPATCH_T(dtype, (rmsnorm_kernel<T><<<m_max, 256, 0, s>>>((const T*)x, (const T*)weight, (T*)y, m_max, m_dev, H, eps,
+                                                                vectorised)));
   RD_CHECK_LAUNCH();
   return RD_OK;
 }
@@ -215,6 +259,12 @@ extern "C" int rd_rope_kv_write(int dtype, const void* qkv, void* q_out, void* k
                                 const int32_t* m_dev, int nh, int nkv, int hd, int max_len, void* stream) {
   RD_REQUIRE(qkv && q_out && k_cache && v_cache && tok_row && tok_pos && tok_slot && cos_table && sin_table, RD_ERR_ARG);
   RD_REQUIRE(m_max >= 1 && nh >= 1 && nkv >= 1 && hd >= 2 && hd % 2 == 0 && max_len >= 1 && n_pos >= 1, RD_ERR_SIZE);
+  {
+    // 16-byte vector accesses: half a head must be a whole number of vectors and every base aligned
+    const int vec = dtype == RD_F32 ? 4 : 8;
+    RD_REQUIRE((hd / 2) % vec == 0, RD_ERR_ALIGN);
+    RD_REQUIRE(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0, RD_ERR_ALIGN);
+  }
   cudaStream_t s = (cudaStream_t)stream;
   RD_DISPATCH_T(dtype, (rope_kv_write_kernel<T><<<m_max, 256, 0, s>>>((const T*)qkv, (T*)q_out, (T*)k_cache, (T*)v_cache,
                                                                       tok_row, tok_pos, tok_slot, cos_table, sin_table,
