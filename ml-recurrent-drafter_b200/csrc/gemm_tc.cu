@@ -156,49 +156,144 @@ struct EpiArgs {
   int64_t ldr;
 };
 
-// 32 consecutive accumulator columns of one TMEM lane = 32 tokens [tok0, tok0+32) of output
-// feature n.  All lanes of the warp run this together (the SwiGLU pairing shuffles).
-template <int EPI, bool OUT_F32>
-__device__ __forceinline__ void epilogue_store(const uint32_t* acc_bits, const EpiArgs& e, int n, int tok0, int M /*token limit*/, int N) {
-  const bool n_ok = n < N;
-  float bias = 0.f;
-  if (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES)
-    bias = n_ok ? __bfloat162float(e.bias[n]) : 0.f;
+constexpr int kScrLd = 36;  // floats per scratch row: 16-byte aligned rows, conflict-free float4 reads
+
+// Element-wise part of the epilogue in accumulator layout (lane = output feature n, i = token).
+template <int EPI>
+__device__ __forceinline__ void epilogue_math(float* v, const EpiArgs& e, int n, int N) {
+  if (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) {
+    const float bias = n < N ? __bfloat162float(e.bias[n]) : 0.f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const int tok = tok0 + i;
-    float v = __uint_as_float(acc_bits[i]) + bias;
-    if (EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) v = rd::silu_f(v);
-    if (EPI == RD_EPI_SWIGLU) {
-      // weight rows (2i, 2i+1) = (gate_i, up_i) sit in adjacent lanes
-      const float up = __shfl_xor_sync(0xffffffffu, v, 1);
-      if ((n & 1) == 0 && tok < M && n + 1 < N) {
-        const float o = rd::silu_f(v) * up;
-        if (OUT_F32)
-          ((float*)e.C)[(int64_t)tok * e.ldc + (n >> 1)] = o;
-        else
-          ((__nv_bfloat16*)e.C)[(int64_t)tok * e.ldc + (n >> 1)] = __float2bfloat16_rn(o);
-      }
-      continue;
+    for (int i = 0; i < 32; ++i) v[i] += bias;
+  }
+  if (EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = rd::silu_f(v[i]);
+  }
+  if (EPI == RD_EPI_SWIGLU) {
+    // weight rows (2i, 2i+1) = (gate_i, up_i) sit in adjacent lanes; even lanes keep the product
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float up = __shfl_xor_sync(0xffffffffu, v[i], 1);
+      v[i] = rd::silu_f(v[i]) * up;
     }
-    if (tok < M && n_ok) {
-      if (OUT_F32) {
-        if (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES) v += ((const float*)e.R)[(int64_t)tok * e.ldr + n];
-        ((float*)e.C)[(int64_t)tok * e.ldc + n] = v;
-      } else {
-        if (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES)
-          v += __bfloat162float(((const __nv_bfloat16*)e.R)[(int64_t)tok * e.ldr + n]);
-        ((__nv_bfloat16*)e.C)[(int64_t)tok * e.ldc + n] = __float2bfloat16_rn(v);
+  }
+}
+
+// Residual values of one token row: kOut consecutive output features starting at column n0.
+template <bool OUT_F32, int kOut>
+struct ResidualRegs {
+  uint4 q[OUT_F32 ? kOut / 4 : kOut / 8];
+  __device__ __forceinline__ void load(const EpiArgs& e, int tok, int n0, bool live) {
+    constexpr int nq = OUT_F32 ? kOut / 4 : kOut / 8;
+    if (live) {
+      const uint4* src = OUT_F32 ? reinterpret_cast<const uint4*>((const float*)e.R + (int64_t)tok * e.ldr + n0)
+                                 : reinterpret_cast<const uint4*>((const __nv_bfloat16*)e.R + (int64_t)tok * e.ldr + n0);
+#pragma unroll
+      for (int j = 0; j < nq; ++j) q[j] = src[j];
+    }
+  }
+  __device__ __forceinline__ void add_to(float* o) const {
+    if (OUT_F32) {
+      const float* f = reinterpret_cast<const float*>(q);
+#pragma unroll
+      for (int j = 0; j < kOut; ++j) o[j] += f[j];
+    } else {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(q);
+#pragma unroll
+      for (int j = 0; j < kOut / 2; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        o[2 * j] += f.x;
+        o[2 * j + 1] += f.y;
       }
     }
   }
+};
+
+// One 32-token block of a tile.  v: accumulator values in (lane = feature, i = token) layout after
+// epilogue_math.  The block is transposed through this warp's scratch so that each lane owns one
+// token and kOut consecutive output features, then written (and the residual read) with 16-byte
+// accesses.  `vec_ok` is false for ragged feature ranges or unaligned outputs: plain stores then.
+template <int EPI, bool OUT_F32>
+__device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float* scr, int lane, int n_warp0, int tok0,
+                                               int tok_limit, int N, bool vec_ok,
+                                               const ResidualRegs<OUT_F32, (EPI == RD_EPI_SWIGLU ? 16 : 32)>& res) {
+  constexpr int kOut = (EPI == RD_EPI_SWIGLU) ? 16 : 32;  // output features per token of this warp
+  constexpr bool kRes = (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES);
+  const int out0 = (EPI == RD_EPI_SWIGLU) ? (n_warp0 >> 1) : n_warp0;  // first output column of the warp
+  const int n_out_total = (EPI == RD_EPI_SWIGLU) ? (N >> 1) : N;
+  if (!vec_ok) {
+    // feature-per-lane fallback
+    const int n = n_warp0 + lane;
+    const bool writer = (EPI == RD_EPI_SWIGLU) ? ((lane & 1) == 0 && n + 1 < N) : (n < N);
+    const int col = (EPI == RD_EPI_SWIGLU) ? (n >> 1) : n;
+    if (writer) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int tok = tok0 + i;
+        if (tok < tok_limit) {
+          float o = v[i];
+          if (OUT_F32) {
+            if (kRes) o += ((const float*)e.R)[(int64_t)tok * e.ldr + col];
+            ((float*)e.C)[(int64_t)tok * e.ldc + col] = o;
+          } else {
+            if (kRes) o += __bfloat162float(((const __nv_bfloat16*)e.R)[(int64_t)tok * e.ldr + col]);
+            ((__nv_bfloat16*)e.C)[(int64_t)tok * e.ldc + col] = __float2bfloat16_rn(o);
+          }
+        }
+      }
+    }
+    return;
+  }
+  // transpose: scr[token i][feature]
+  if (EPI == RD_EPI_SWIGLU) {
+    if ((lane & 1) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) scr[i * kScrLd + (lane >> 1)] = v[i];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = v[i];
+  }
+  __syncwarp();
+  float o[kOut];
+#pragma unroll
+  for (int j = 0; j < kOut / 4; ++j) {
+    const float4 f = *reinterpret_cast<const float4*>(scr + lane * kScrLd + 4 * j);
+    o[4 * j] = f.x;
+    o[4 * j + 1] = f.y;
+    o[4 * j + 2] = f.z;
+    o[4 * j + 3] = f.w;
+  }
+  __syncwarp();  // the scratch is reused by the next block
+  const int tok = tok0 + lane;
+  if (tok < tok_limit) {
+    if (kRes) res.add_to(o);
+    if (OUT_F32) {
+      float4* dst = reinterpret_cast<float4*>((float*)e.C + (int64_t)tok * e.ldc + out0);
+#pragma unroll
+      for (int j = 0; j < kOut / 4; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+    } else {
+      uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)e.C + (int64_t)tok * e.ldc + out0);
+#pragma unroll
+      for (int j = 0; j < kOut / 8; ++j) {
+        uint4 pk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(o[8 * j + 2 * t], o[8 * j + 2 * t + 1]);
+        dst[j] = pk;
+      }
+    }
+  }
+  (void)n_out_total;
 }
 
 struct SmemLayout {
   static constexpr int kStageW = BM * BK * 2;         // 16 KB
   static constexpr int kStageA = kMaxChunk * BK * 2;  // 32 KB: two 128-token boxes back to back
   static constexpr int kStages = 4;
-  static constexpr int kBytes = kStages * (kStageW + kStageA) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kScratch = 4 * 32 * kScrLd * 4;  // per-epilogue-warp transpose scratch
+  static constexpr int kBytes = kStages * (kStageW + kStageA) + kScratch + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 template <int EPI, bool OUT_F32>
@@ -211,7 +306,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sW = smem;
   uint8_t* sA = smem + kStages * L::kStageW;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (L::kStageW + L::kStageA));
+  float* scratch = reinterpret_cast<float*>(smem + kStages * (L::kStageW + L::kStageA));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (L::kStageW + L::kStageA) + L::kScratch);
   uint64_t* full = bars;                    // [kStages]
   uint64_t* empty = bars + kStages;         // [kStages]
   uint64_t* acc_full = bars + 2 * kStages;  // [2]
@@ -327,6 +423,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ---------------- epilogue warps ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    float* scr = scratch + (warp - 2) * 32 * kScrLd;
+    constexpr int kOut = (EPI == RD_EPI_SWIGLU) ? 16 : 32;
+    constexpr bool kRes = (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES);
+    const int esz = OUT_F32 ? 4 : 2;
+    const bool aligned = (((uintptr_t)epi.C | (uintptr_t)(kRes ? epi.R : epi.C)) % 16 == 0) && ((epi.ldc * esz) % 16 == 0) &&
+                         (!kRes || (epi.ldr * esz) % 16 == 0);
     bool ok = true;
     int local = 0;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
@@ -335,20 +437,32 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int tok_base = ci * ch.chunk;
       // tokens past the chunk belong to the next chunk's tile (its columns here were not computed)
       const int tok_limit = min(M, tok_base + ch.chunk);
+      const int n_warp0 = w_tile * BM + quarter * 32;
+      const bool vec_ok = aligned && (n_warp0 + 32 <= N);
+      const int out0 = (EPI == RD_EPI_SWIGLU) ? (n_warp0 >> 1) : n_warp0;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      // the first block's residual row is fetched while the main loop of this tile still runs
+      ResidualRegs<OUT_F32, kOut> res_next;
+      if (kRes && vec_ok) res_next.load(epi, tok_base + lane, out0, tok_base + lane < tok_limit);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int n = w_tile * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
 #pragma unroll 1
       for (int c = 0; c < cols; c += 32) {
+        ResidualRegs<OUT_F32, kOut> res_cur = res_next;
+        if (kRes && vec_ok && c + 32 < cols)
+          res_next.load(epi, tok_base + c + 32 + lane, out0, tok_base + c + 32 + lane < tok_limit);
         uint32_t r[32];
         tmem_ld32(t_row + c, r);
-        epilogue_store<EPI, OUT_F32>(r, epi, n, tok_base + c, tok_limit, N);
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        epilogue_math<EPI>(v, epi, n_warp0 + lane, N);
+        epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
       }
       tc_fence_before();
       __syncwarp();
