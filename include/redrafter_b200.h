@@ -38,6 +38,7 @@ extern "C" {
 #define RD_ERR_LAUNCH (-4)      /* the CUDA launch was rejected; see rd_last_cuda_error() */
 #define RD_ERR_ALIGN (-5)       /* pointer or leading dimension not aligned as required */
 #define RD_ERR_UNSUPPORTED (-6) /* combination not implemented */
+#define RD_ERR_CAPACITY (-7)    /* request larger than the fixed capacity of an entry point that cannot allocate */
 
 #define RD_F32 0
 #define RD_BF16 1
@@ -271,6 +272,30 @@ RD_API int rd_emit_tokens(const int64_t* token_buf, int max_len, const int32_t* 
  * for f in [0, n_flat).  scratch must hold NL*2*B*nkv*n_flat*hd elements. */
 RD_API int rd_cache_unpack(int dtype, void* cache, int NL, int B, int nkv, int max_len, int hd, int S,
                     const int64_t* unpacker, int n_flat, void* scratch, void* stream);
+
+/* Same result as rd_cache_unpack, for callers that can give the library no scratch buffer.
+ * This entry point has no counterpart in the reference.
+ *
+ * Who needs it: a host that took all of the device's memory into its own arena at start-up (a
+ * later cudaMalloc from a plug-in simply fails there), or a latency-critical loop whose rules
+ * forbid device allocation after initialisation because cudaMalloc/cudaFree stall the device.
+ * Such a caller passes only the cache and the index; the staging copy of the gathered rows lives
+ * in a fixed array inside the library, RD_STATIC_SCRATCH_BYTES large, which every GPU that loads
+ * the library keeps until the process ends.
+ *
+ * Limits and rules:
+ *   - NL*2*B*nkv*n_flat*hd*sizeof(element) must not exceed RD_STATIC_SCRATCH_BYTES, otherwise the
+ *     call returns RD_ERR_CAPACITY and does nothing;
+ *   - the first call on each device looks the array's device address up (with that device
+ *     current) and remembers it; make that first call during set-up, before any stream capture;
+ *   - nothing in the array has to start at zero (the part in use is overwritten before it is
+ *     read), so it is never cleared and keeps the previous call's bytes;
+ *   - every call uses the same array: two calls whose kernels can run at the same time on one
+ *     GPU (different streams) race and corrupt each other - order them on one stream;
+ *   - no cudaMalloc, cudaFree or other allocating routine is called. */
+#define RD_STATIC_SCRATCH_BYTES (16u << 20)
+RD_API int rd_cache_unpack_static(int dtype, void* cache, int NL, int B, int nkv, int max_len, int hd, int S,
+                                  const int64_t* unpacker, int n_flat, void* stream);
 
 #ifdef __cplusplus
 }

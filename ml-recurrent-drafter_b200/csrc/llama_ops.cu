@@ -217,6 +217,10 @@ __global__ void cache_unpack_scatter_kernel(T* __restrict__ cache, int B, int nk
   for (int d = threadIdx.x; d < hd; d += blockDim.x) dst[d] = src[d];
 }
 
+// Staging array of rd_cache_unpack_static.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a pointer a kernel may be given.
+__device__ __align__(256) unsigned char g_static_unpack_scratch[RD_STATIC_SCRATCH_BYTES];
+
 }  // namespace
 
 #define RD_DISPATCH_T(dtype, ...)                  \
@@ -308,6 +312,46 @@ extern "C" int rd_cache_unpack(int dtype, void* cache, int NL, int B, int nkv, i
   RD_REQUIRE(NL >= 1 && B >= 1 && nkv >= 1 && hd >= 1 && S >= 0 && n_flat >= 1 && S + n_flat <= max_len &&
                  (int64_t)B * nkv <= 65535 && NL * 2 <= 65535,
              RD_ERR_SIZE);
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(n_flat, B * nkv, NL * 2);
+  RD_DISPATCH_T(dtype, {
+    cache_unpack_gather_kernel<T><<<grid, 64, 0, s>>>((const T*)cache, B, nkv, max_len, hd, S, unpacker, n_flat, (T*)scratch);
+    cache_unpack_scatter_kernel<T><<<grid, 64, 0, s>>>((T*)cache, B, nkv, max_len, hd, S, n_flat, (const T*)scratch);
+  });
+  RD_CHECK_LAUNCH();
+  return RD_OK;
+}
+
+// Device address of g_static_unpack_scratch per device ordinal, looked up on the first call made
+// with that device current.  Looking it up twice from two host threads yields the same value.
+static void* g_static_scratch_addr[64] = {};
+
+extern "C" int rd_cache_unpack_static(int dtype, void* cache, int NL, int B, int nkv, int max_len, int hd, int S,
+                                      const int64_t* unpacker, int n_flat, void* stream) {
+  RD_REQUIRE(cache && unpacker, RD_ERR_ARG);
+  RD_REQUIRE(dtype == RD_F32 || dtype == RD_BF16, RD_ERR_DTYPE);
+  RD_REQUIRE(NL >= 1 && B >= 1 && nkv >= 1 && hd >= 1 && S >= 0 && n_flat >= 1 && S + n_flat <= max_len &&
+                 (int64_t)B * nkv <= 65535 && NL * 2 <= 65535,
+             RD_ERR_SIZE);
+  const size_t esz = dtype == RD_F32 ? 4 : 2;
+  const size_t need = (size_t)NL * 2 * B * nkv * n_flat * hd * esz;
+  RD_REQUIRE(need <= (size_t)RD_STATIC_SCRATCH_BYTES, RD_ERR_CAPACITY);
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= 64) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    err = cudaGetSymbolAddress(&p, g_static_unpack_scratch);
+    if (err != cudaSuccess || p == nullptr) {
+      rd_set_last_cuda_error((int)err);
+      return RD_ERR_LAUNCH;
+    }
+    g_static_scratch_addr[dev] = p;
+  }
+  void* scratch = g_static_scratch_addr[dev];
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(n_flat, B * nkv, NL * 2);
   RD_DISPATCH_T(dtype, {

@@ -21,6 +21,7 @@ extern "C" const char* rd_strerror(int code) {
     case RD_ERR_LAUNCH: return "CUDA launch rejected (see rd_last_cuda_error)";
     case RD_ERR_ALIGN: return "pointer or leading dimension misaligned";
     case RD_ERR_UNSUPPORTED: return "combination not implemented";
+    case RD_ERR_CAPACITY: return "request exceeds the fixed capacity of this entry point (it cannot allocate)";
     default: return "unknown error code";
   }
 }

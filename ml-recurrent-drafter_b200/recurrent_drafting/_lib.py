@@ -17,6 +17,7 @@ F32, BF16 = 0, 1
 EPI_NONE, EPI_BIAS, EPI_BIAS_SILU, EPI_BIAS_SILU_RES, EPI_RES, EPI_SWIGLU = range(6)
 ATTN_CAUSAL, ATTN_TREE, ATTN_DENSE = 0, 1, 2
 TOPK_MAX_KEPT = 64
+STATIC_SCRATCH_BYTES = 16 << 20
 MAX_BEAM_WIDTH = 64
 MAX_BEAM_LENGTH = 8
 
@@ -51,6 +52,7 @@ SIGNATURES = {
     "rd_sample_from_sparse": (_I, [_P, _P, _P, _I, _P, _P, _P]),
     "rd_emit_tokens": (_I, [_P, _I, _P, _P, _P, _L, _I, _I, _P, _P]),
     "rd_cache_unpack": (_I, [_I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
+    "rd_cache_unpack_static": (_I, [_I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P]),
 }
 
 _lib = None

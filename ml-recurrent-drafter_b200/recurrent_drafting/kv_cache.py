@@ -69,3 +69,22 @@ class Cache:
                   n_heads, max_length, head_dim, prompt_length, _lib.ptr(idx), n_flat, _lib.ptr(scratch), _lib.stream())
         for k, v in self.sliced:
             k.length = v.length = prompt_length + n_flat
+
+    def unpack_static(self, prompt_length: int, tree_attn_index: torch.Tensor) -> None:
+        """Cache.unpack for callers that must not allocate device memory (a host that owns all of the
+        device's memory in its own arena, or a loop that forbids allocation after set-up): the staging
+        copy lives in a fixed 16 MiB array inside the library instead of a fresh tensor.
+
+        tree_attn_index must already be a contiguous int64 tensor of shape (cache batch, W, Lb) on the
+        cache's device, so that this wrapper creates no tensor either.  Raises if the gathered rows
+        (n_layers*2*batch*heads*W*Lb*head_dim elements) do not fit; calls that can overlap on the GPU
+        share the array and must be ordered on one stream; make the first call per device at set-up.
+        """
+        n_layers, _, cache_batch, n_heads, max_length, head_dim = self._cache.shape
+        idx = tree_attn_index
+        assert idx.dtype == torch.int64 and idx.is_contiguous() and idx.shape[0] == cache_batch
+        n_flat = idx.shape[1] * idx.shape[2]
+        _lib.call("rd_cache_unpack_static", _lib.dtype_code(self._cache.dtype), _lib.ptr(self._cache), n_layers, cache_batch,
+                  n_heads, max_length, head_dim, prompt_length, _lib.ptr(idx), n_flat, _lib.stream())
+        for k, v in self.sliced:
+            k.length = v.length = prompt_length + n_flat
