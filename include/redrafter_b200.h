@@ -198,6 +198,19 @@ RD_API int rd_attention(int dtype, const void* q, const void* k_cache, const voi
                  int hd, int max_len, int max_new, int max_kv, int mode, const uint32_t* tree_mask, int mask_words,
                  const uint8_t* dense_mask, int64_t dense_ld_q, int64_t dense_ld_b, void* stream);
 
+/* The same attention for bf16 and head_dim 128 on the tcgen05 tensor cores (S = Q K^T and O = P V
+ * as tcgen05.mma with TMEM accumulators, K/V tiles staged by TMA).  Modes RD_ATTN_CAUSAL and
+ * RD_ATTN_TREE.  `plan` is a host pointer from rd_attention_plan_create, which encodes the TMA
+ * descriptors of these exact buffers: q [m_max, nh*128], k_cache / v_cache [B, nkv, max_len, 128]
+ * (host memory only; free with rd_attention_plan_destroy; NULL on failure).  `status` (optional,
+ * device int32) receives a non-zero code if a bounded device-side wait gave up. */
+RD_API void* rd_attention_plan_create(const void* q, int m_max, const void* k_cache, const void* v_cache, int B, int nh,
+                                      int nkv, int hd, int max_len);
+RD_API void rd_attention_plan_destroy(void* plan);
+RD_API int rd_attention_tc(const void* plan, void* out, const int32_t* row_start, const int32_t* kv_begin,
+                           const int32_t* base_len, int max_new, int mode, const uint32_t* tree_mask, int mask_words,
+                           int32_t* status, void* stream);
+
 /* argmax_v logits[t, v], first maximal index (torch.argmax, recurrent_drafting.py:52), written
  * to out32 [M] and/or out64 [M] (either may be NULL). */
 RD_API int rd_argmax_rows(const float* logits, int64_t ld, int m_max, const int32_t* m_dev, int V, int32_t* out32,

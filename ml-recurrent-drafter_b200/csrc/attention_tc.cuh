@@ -1,8 +1,9 @@
 // bf16 flash attention of new tokens over a per-row KV cache (cached prefix + causal or
 // prefix-tree visibility among the new tokens), tensor-core path.
 //
-// One CTA = 4 warps = 64 queries of one (batch row, head); each warp owns 16 queries.  K/V tiles
-// of 64 keys stream through a two-stage cp.async pipeline in XOR-swizzled shared memory; S = Q K^T
+// One CTA = 8 warps = 128 queries of one (batch row, head) - normally all the packed tree tokens
+// of the row, so that K/V are read once per (row, head); each warp owns 16 queries.  K/V tiles of
+// 64 keys stream through a three-stage cp.async pipeline in XOR-swizzled shared memory; S = Q K^T
 // and O += P V run on mma.sync m16n8k16 (bf16 in, fp32 accumulate) with ldmatrix-fed fragments;
 // the softmax is the online (running max / running sum) form in the exp2 domain.  Tiles that lie
 // wholly inside the cached prefix skip the mask; tiles overlapping the new tokens read the tree
@@ -12,9 +13,10 @@
 
 namespace rd_attn {
 
-constexpr int kBM = 64;  // queries per CTA
+constexpr int kBM = 128;  // queries per CTA
 constexpr int kBN = 64;  // keys per tile
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;
+constexpr int kStages = 3;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -58,7 +60,7 @@ template <int HD>
 struct Smem {
   static constexpr int kTile = kBN * HD * 2;           // one K or V tile
   static constexpr int kQ = kBM * HD * 2;              // the Q tile
-  static constexpr int kBytes = kQ + 4 * kTile;        // Q + 2 stages x (K, V)
+  static constexpr int kBytes = kQ + 2 * kStages * kTile;  // Q + stages x (K, V)
 };
 
 template <int HD>
@@ -117,8 +119,15 @@ __global__ void __launch_bounds__(kThreads) attention_tc_kernel(
       }
     }
   }
+  // prologue: tiles 0 and 1 in flight (every iteration commits exactly one group, empty or not,
+  // so that "all but the newest group" always means "tile `it` has landed")
   load_tile<HD>(sKV, kbase, 0, kv_end, tid);
   load_tile<HD>(sKV + Smem<HD>::kTile, vbase, 0, kv_end, tid);
+  cp_async_commit();
+  if (n_tiles > 1) {
+    load_tile<HD>(sKV + 2 * Smem<HD>::kTile, kbase, kBN, kv_end, tid);
+    load_tile<HD>(sKV + 3 * Smem<HD>::kTile, vbase, kBN, kv_end, tid);
+  }
   cp_async_commit();
 
   uint32_t qf[HD / 16][4];
@@ -129,17 +138,15 @@ __global__ void __launch_bounds__(kThreads) attention_tc_kernel(
   const int qi0 = q0 + warp * 16 + g;  // this thread's query rows: qi0 and qi0 + 8
 
   for (int it = 0; it < n_tiles; ++it) {
-    const int stage = it & 1;
-    if (it + 1 < n_tiles) {
-      uint8_t* dst = sKV + (stage ^ 1) * 2 * Smem<HD>::kTile;
-      load_tile<HD>(dst, kbase, (it + 1) * kBN, kv_end, tid);
-      load_tile<HD>(dst + Smem<HD>::kTile, vbase, (it + 1) * kBN, kv_end, tid);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    const int stage = it % kStages;
+    cp_async_wait<1>();
+    __syncthreads();  // tile `it` visible to all; everyone is done with tile it-1, whose stage is refilled next
+    if (it + 2 < n_tiles) {
+      uint8_t* dst = sKV + ((it + 2) % kStages) * 2 * Smem<HD>::kTile;
+      load_tile<HD>(dst, kbase, (it + 2) * kBN, kv_end, tid);
+      load_tile<HD>(dst + Smem<HD>::kTile, vbase, (it + 2) * kBN, kv_end, tid);
     }
-    __syncthreads();
+    cp_async_commit();
     if (it == 0) {
       // Q fragments stay in registers for the whole kernel
 #pragma unroll
@@ -253,8 +260,8 @@ __global__ void __launch_bounds__(kThreads) attention_tc_kernel(
         mma_bf16(o[db + 1], pf[kb], b2, b3);
       }
     }
-    __syncthreads();  // the stage is overwritten by the next iteration's prefetch
   }
+  cp_async_wait<0>();
 
   // finalise: divide by the row sums (summed over the quad) and store bf16
 #pragma unroll

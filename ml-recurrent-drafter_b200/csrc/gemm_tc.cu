@@ -23,6 +23,7 @@
 // Every mbarrier wait is bounded: when a wait gives up the kernel records a code in *status,
 // stops issuing work, lets outstanding bulk copies land, frees its TMEM and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "rd_common.cuh"
 
@@ -34,6 +35,12 @@ constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr uint32_t kSpinLimit = 1u << 22;  // polls, each followed by a short sleep
+
+// Experiment switch: 0 forces the single-CTA kernel (environment RD_GEMM_PAIRS=0, read once).
+static int g_use_pairs = [] {
+  const char* v = getenv("RD_GEMM_PAIRS");
+  return (v && v[0] == '0') ? 0 : 1;
+}();
 
 struct GemmPlan {
   CUtensorMap map_a;  // activations [m_max, K], box 64 x 128
@@ -479,6 +486,256 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+
+// =================================================================================================
+// CTA-pair variant (cta_group::2): two CTAs of a cluster share one MMA of M = 256 weight rows.
+// Each CTA stages its own 128 weight rows and HALF of the token tile, so the shared-memory traffic
+// per MMA drops by a third and the per-CTA L2 traffic by the same; the leader CTA's elected thread
+// issues the MMAs for both, each CTA's TMEM receives its 128 rows of the accumulator, and each
+// CTA's epilogue warps store their own rows.  Signalling: both CTAs' bulk loads complete on the
+// LEADER's full barrier; the leader frees a stage and publishes an accumulator with one
+// tcgen05.commit per CTA (plain commits to a local and to a peer barrier, no multicast); the
+// peer's epilogue warps release the accumulator with remote arrives on the leader's barrier.
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t leader_bar_cluster_addr, int c0,
+                                                 int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+          "r"(smem_u32(dst)),
+      "l"(map), "r"(leader_bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t umma_instr_desc_pair(int n) {
+  // fp32 accumulator, bf16 A and B, both K-major, M = 256 over the CTA pair, N = n
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+struct SmemLayoutPair {
+  static constexpr int kStageW = BM * BK * 2;   // 16 KB: this CTA's 128 weight rows
+  static constexpr int kStageA = 128 * BK * 2;  // 16 KB: this CTA's half of the token tile
+  static constexpr int kStages = 6;
+  static constexpr int kScratch = 4 * 32 * kScrLd * 4;
+  static constexpr int kBytes = kStages * (kStageW + kStageA) + kScratch + 1024 + 256;
+};
+
+template <int EPI, bool OUT_F32>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, EpiArgs epi,
+                        int m_max, const int32_t* __restrict__ m_dev, int N, int K, int32_t* status) {
+  using L = SmemLayoutPair;
+  constexpr int kStages = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sW = smem;
+  uint8_t* sA = smem + kStages * L::kStageW;
+  float* scratch = reinterpret_cast<float*>(smem + kStages * (L::kStageW + L::kStageA));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (L::kStageW + L::kStageA) + L::kScratch);
+  uint64_t* full = bars;                    // [kStages] used in the leader CTA
+  uint64_t* empty = bars + kStages;         // [kStages] one per CTA
+  uint64_t* acc_full = bars + 2 * kStages;  // [2] one per CTA
+  uint64_t* acc_empty = acc_full + 2;       // [2] used in the leader CTA (8 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int M = rd::live_rows(m_dev, m_max);
+  const Chunking ch = make_chunking(M);
+  const int w_pairs = (N + 2 * BM - 1) / (2 * BM);
+  const int total_tiles = M > 0 ? w_pairs * ch.n_chunks : 0;
+  const int k_blocks = K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(2 * kMaxChunk)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs) {
+        const int w_pair = tile / ch.n_chunks, ci = tile % ch.n_chunks;
+        const int cols = chunk_cols(ch, ci, M);
+        const int tok0 = ci * ch.chunk + (int)rank * (cols >> 1);  // this CTA's half of the chunk
+        const int w_row0 = w_pair * 2 * BM + (int)rank * BM;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t leader_full = mapa_u32(smem_u32(&full[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * (L::kStageW + L::kStageA));
+          tma_load_2d_pair(sW + stage * L::kStageW, &map_w, leader_full, kb * BK, w_row0);
+          tma_load_2d_pair(sA + stage * L::kStageA, &map_a, leader_full, kb * BK, tok0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        if (atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 11);
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs, ++local) {
+        const int ci = tile % ch.n_chunks;
+        const uint32_t idesc = umma_instr_desc_pair(chunk_cols(ch, ci, M));
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kMaxChunk;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t dw = umma_smem_desc(smem_u32(sW + stage * L::kStageW));
+          const uint64_t da = umma_smem_desc(smem_u32(sA + stage * L::kStageA));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma_f16_pair(d_tmem, dw + 2 * k, da + 2 * k, idesc, (kb | k) != 0);
+          // free the stage in both CTAs
+          umma_commit_pair(smem_u32(&empty[stage]));
+          umma_commit_pair(mapa_u32(smem_u32(&empty[stage]), 1));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) {
+          umma_commit_pair(smem_u32(&acc_full[acc]));
+          umma_commit_pair(mapa_u32(smem_u32(&acc_full[acc]), 1));
+        }
+      }
+      if (!ok && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 12);
+    }
+  } else {
+    // ---------------- epilogue warps (both CTAs, own 128 weight rows) ----------------
+    const int quarter = warp & 3;
+    float* scr = scratch + (warp - 2) * 32 * kScrLd;
+    constexpr int kOut = (EPI == RD_EPI_SWIGLU) ? 16 : 32;
+    constexpr bool kRes = (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES);
+    const int esz = OUT_F32 ? 4 : 2;
+    const bool aligned = (((uintptr_t)epi.C | (uintptr_t)(kRes ? epi.R : epi.C)) % 16 == 0) && ((epi.ldc * esz) % 16 == 0) &&
+                         (!kRes || (epi.ldr * esz) % 16 == 0);
+    bool ok = true;
+    int local = 0;
+    for (int tile = pair_id; ok && tile < total_tiles; tile += n_pairs, ++local) {
+      const int w_pair = tile / ch.n_chunks, ci = tile % ch.n_chunks;
+      const int cols = chunk_cols(ch, ci, M);
+      const int tok_base = ci * ch.chunk;
+      const int tok_limit = min(M, tok_base + ch.chunk);
+      const int n_warp0 = w_pair * 2 * BM + (int)rank * BM + quarter * 32;
+      const bool vec_ok = aligned && (n_warp0 + 32 <= N);
+      const int out0 = (EPI == RD_EPI_SWIGLU) ? (n_warp0 >> 1) : n_warp0;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ResidualRegs<OUT_F32, kOut> res_next;
+      if (kRes && vec_ok) res_next.load(epi, tok_base + lane, out0, tok_base + lane < tok_limit);
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
+#pragma unroll 1
+      for (int c = 0; c < cols; c += 32) {
+        ResidualRegs<OUT_F32, kOut> res_cur = res_next;
+        if (kRes && vec_ok && c + 32 < cols)
+          res_next.load(epi, tok_base + c + 32 + lane, out0, tok_base + c + 32 + lane < tok_limit);
+        uint32_t r[32];
+        tmem_ld32(t_row + c, r);
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        epilogue_math<EPI>(v, epi, n_warp0 + lane, N);
+        epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[acc]), 0));
+    }
+    if (!ok && lane == 0 && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 13);
+  }
+
+  // Neither CTA may leave (or free TMEM) while its peer can still signal its barriers or while
+  // MMAs of the pair are in flight: meet at a cluster barrier first.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kMaxChunk) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -507,9 +764,32 @@ bool make_map(CUtensorMap* map, const void* base, int64_t ld_elems, int rows, in
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <typename Kern>
+int launch_cluster2(Kern kern, int grid, int smem_bytes, cudaStream_t s, const GemmPlan* p, const EpiArgs& e, const int32_t* m_dev,
+                    int32_t* status) {
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t err = cudaLaunchKernelEx(&cfg, kern, p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K, status);
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
+  return RD_OK;
+}
+
 template <int EPI>
 int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t* m_dev, int32_t* status, cudaStream_t s) {
-  using L = SmemLayout;
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
@@ -517,7 +797,23 @@ int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const int tiles = ((p->m_max + kMaxChunk - 1) / kMaxChunk) * ((p->N + BM - 1) / BM);
+  const int chunks = (p->m_max + kMaxChunk - 1) / kMaxChunk;
+  if (p->N >= 2 * BM && g_use_pairs) {
+    // CTA pairs: one pair per 256 weight rows x token chunk
+    const int tiles = chunks * ((p->N + 2 * BM - 1) / (2 * BM));
+    const int max_pairs = sm_count / 2;
+    const int grid = 2 * (tiles < max_pairs ? tiles : max_pairs);
+    int rc;
+    if (out_dtype == RD_F32)
+      rc = launch_cluster2(gemm_tc_pair_kernel<EPI, true>, grid, SmemLayoutPair::kBytes, s, p, e, m_dev, status);
+    else
+      rc = launch_cluster2(gemm_tc_pair_kernel<EPI, false>, grid, SmemLayoutPair::kBytes, s, p, e, m_dev, status);
+    if (rc != RD_OK) return rc;
+    RD_CHECK_LAUNCH();
+    return RD_OK;
+  }
+  using L = SmemLayout;
+  const int tiles = chunks * ((p->N + BM - 1) / BM);
   const int grid = tiles < sm_count ? tiles : sm_count;
   if (out_dtype == RD_F32) {
     auto kern = gemm_tc_kernel<EPI, true>;

@@ -42,7 +42,8 @@ struct Num<__nv_bfloat16> {
   static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+// fast form for rounded (bf16) outputs: approximate exp and division, ~2 ulp
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 // expf with full fp32 accuracy (used where parity with a CPU fp32 path matters)
 __device__ __forceinline__ float silu_exact(float x) { return x / (1.0f + expf(-x)); }
 

@@ -42,6 +42,9 @@ SIGNATURES = {
     "rd_rmsnorm": (_I, [_I, _P, _P, _P, _I, _P, _I, _F, _P]),
     "rd_rope_kv_write": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P]),
     "rd_attention": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _L, _L, _P]),
+    "rd_attention_plan_create": (_P, [_P, _I, _P, _P, _I, _I, _I, _I, _I]),
+    "rd_attention_plan_destroy": (None, [_P]),
+    "rd_attention_tc": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P]),
     "rd_argmax_rows": (_I, [_P, _L, _I, _P, _I, _P, _P, _P]),
     "rd_accept_commit_greedy": (_I, [_I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "rd_commit_reference_slots": (_I, [_I, _I, _I, _P, _P, _P, _I, _I, _P, _P]),

@@ -135,6 +135,7 @@ class LlamaForCausalLM(nn.Module):
         self._ws: Dict[Tuple, Dict[str, torch.Tensor]] = {}
         self._linears = None
         self._rope = None
+        self._attn_plans: Dict[Tuple, int] = {}
         self.gemm_status: Optional[torch.Tensor] = None
 
     # ----------------------------------------------------------------- reference-compatible surface
@@ -224,6 +225,43 @@ class LlamaForCausalLM(nn.Module):
         self._linears = None
         self._ws = {}
         self._rope = None
+        self._drop_attn_plans()
+
+    def _drop_attn_plans(self):
+        plans = getattr(self, "_attn_plans", None)
+        if plans:
+            lib = _lib.load()
+            for p in plans.values():
+                lib.rd_attention_plan_destroy(p)
+        self._attn_plans = {}
+
+    def __del__(self):
+        try:
+            self._drop_attn_plans()
+        except Exception:
+            pass
+
+    def _attention(self, code, q, kc, vc, attn, row_start, kv_begin, base_len, batch, m_max, max_new, max_kv, mode, tree_mask,
+                   mask_words, dense_mask, dld_q, dld_b, st):
+        nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        max_len = kc.shape[2]
+        if self.dtype == torch.bfloat16 and hd == 128 and mode != _lib.ATTN_DENSE and mask_words <= 16:
+            # tcgen05 path: TMA descriptors are tied to these exact buffers
+            key = (q.data_ptr(), m_max, kc.data_ptr(), vc.data_ptr(), batch, max_len)
+            plan = self._attn_plans.get(key)
+            if plan is None:
+                plan = _lib.load().rd_attention_plan_create(_lib.ptr(q), m_max, _lib.ptr(kc), _lib.ptr(vc), batch, nh, nkv, hd, max_len)
+                if not plan:
+                    raise _lib.RedrafterError("rd_attention_plan_create failed (TMA descriptor could not be encoded)")
+                if len(self._attn_plans) > 4096:
+                    self._drop_attn_plans()
+                self._attn_plans[key] = plan
+            _lib.call("rd_attention_tc", plan, _lib.ptr(attn), _lib.ptr(row_start), _lib.ptr(kv_begin), _lib.ptr(base_len), max_new,
+                      mode, _lib.ptr(tree_mask), mask_words, _lib.ptr(self.gemm_status), st)
+            return
+        _lib.call("rd_attention", code, _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(attn), _lib.ptr(row_start),
+                  _lib.ptr(kv_begin), _lib.ptr(base_len), batch, nh, nkv, hd, max_len, max_new, max_kv, mode,
+                  _lib.ptr(tree_mask), mask_words, _lib.ptr(dense_mask), dld_q, dld_b, st)
 
     # ----------------------------------------------------------------- kernels
     def _lin(self):
@@ -287,9 +325,8 @@ class LlamaForCausalLM(nn.Module):
             _lib.call("rd_rope_kv_write", code, _lib.ptr(qkv), _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(tok_row),
                       _lib.ptr(tok_pos), _lib.ptr(tok_slot), _lib.ptr(cos), _lib.ptr(sin), cos.shape[0], m_max, md, nh, nkv,
                       hd, max_len, st)
-            _lib.call("rd_attention", code, _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(attn), _lib.ptr(row_start),
-                      _lib.ptr(kv_begin), _lib.ptr(base_len), batch, nh, nkv, hd, max_len, max_new, max_kv, mode,
-                      _lib.ptr(tree_mask), mask_words, _lib.ptr(dense_mask), dld_q, dld_b, st)
+            self._attention(code, q, kc, vc, attn, row_start, kv_begin, base_len, batch, m_max, max_new, max_kv, mode, tree_mask,
+                            mask_words, dense_mask, dld_q, dld_b, st)
             lin["o"][l](attn, h, _lib.EPI_RES, residual=h, m_dev=m_dev, m_max=m_max, status=self.gemm_status)
             _lib.call("rd_rmsnorm", code, _lib.ptr(h), _lib.ptr(self.ln2[l]), _lib.ptr(xn), m_max, md, H, self.eps, st)
             lin["gu"][l](xn, act, _lib.EPI_SWIGLU, m_dev=m_dev, m_max=m_max, status=self.gemm_status)

@@ -153,3 +153,55 @@ def test_state_dict_round_trip():
     for k, v in lw.items():
         assert np.array_equal(sd[k].cpu().numpy(), v), k
     assert set(dr.state_dict().keys()) == set(dw.keys())
+
+
+@pytest.mark.parametrize("mode", ["causal", "tree"])
+@pytest.mark.parametrize("W,L,bases", [(45, 5, (10, 70, 133)), (8, 3, (0, 1, 64)), (64, 7, (300, 5, 129))])
+def test_attention_tcgen05(mode, W, L, bases):
+    """The tcgen05 attention (TMA + TMEM) against the fp32 oracle: ragged rows, several query tiles
+    (n_new > 128), prefixes that end inside, at and before a key-tile boundary, GQA."""
+    from recurrent_drafting import _lib
+
+    rs = np.random.RandomState(W * 10 + L)
+    B, nh, nkv, hd, max_len = 3, 4, 2, 128, 900
+    beams = mb.zipf_beams(B, W, L, 5000, 7)
+    pt = ota.dedup_prefix(beams)
+    unp = ota.get_unpacker(beams, pt)
+    _, idx = ota.pack_beams(beams, pt)
+    tree = ota.causal_mask_of_packed_beams(unp, idx)
+    n_new = ota.n_selected(beams).astype(np.int32)
+    kv_begin = np.array([0, 3, 1], dtype=np.int32)
+    base = np.array(bases, dtype=np.int32)
+    row_start = np.concatenate([[0], np.cumsum(n_new)]).astype(np.int32)
+    M = int(row_start[-1])
+    tq = t(rs.standard_normal((M, nh * hd)).astype(np.float32)).bfloat16()
+    tk = t(rs.standard_normal((B, nkv, max_len, hd)).astype(np.float32)).bfloat16()
+    tv = t(rs.standard_normal((B, nkv, max_len, hd)).astype(np.float32)).bfloat16()
+    q, k, v = (x.float().cpu().numpy() for x in (tq, tk, tv))
+    q = q.reshape(M, nh, hd)
+    out = torch.zeros(M, nh * hd, dtype=torch.bfloat16, device="cuda")
+    import recurrent_drafting as rd
+
+    fp = rd.tree_attention.pack_flat(t(beams))
+    t_rs, t_begin, t_base = t(row_start), t(kv_begin), t(base)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib = _lib.load()
+    plan = lib.rd_attention_plan_create(_lib.ptr(tq), M, _lib.ptr(tk), _lib.ptr(tv), B, nh, nkv, hd, max_len)
+    assert plan
+    code = _lib.ATTN_CAUSAL if mode == "causal" else _lib.ATTN_TREE
+    _lib.call("rd_attention_tc", plan, _lib.ptr(out), _lib.ptr(t_rs), _lib.ptr(t_begin), _lib.ptr(t_base), int(n_new.max()), code,
+              _lib.ptr(fp.tree_mask), fp.mask_words, _lib.ptr(status), _lib.stream())
+    torch.cuda.synchronize()
+    lib.rd_attention_plan_destroy(plan)
+    assert int(status.item()) == 0
+    got = out.float().cpu().numpy().reshape(M, nh, hd)
+    for b in range(B):
+        n, s = int(n_new[b]), int(row_start[b])
+        kv = int(base[b]) + n
+        ks = np.repeat(k[b, :, kv_begin[b] : kv_begin[b] + kv], nh // nkv, axis=0)[None]
+        vs = np.repeat(v[b, :, kv_begin[b] : kv_begin[b] + kv], nh // nkv, axis=0)[None]
+        mask = np.zeros((1, n, kv), dtype=bool)
+        mask[0, :, : base[b]] = True
+        mask[0, :, base[b] :] = np.tril(np.ones((n, n), dtype=bool)) if mode == "causal" else tree[b, :n, :n]
+        want = ollama.attention(q[s : s + n].transpose(1, 0, 2)[None], ks, vs, mask)[0].transpose(1, 0, 2)
+        np.testing.assert_allclose(got[s : s + n], want, rtol=2e-2, atol=2e-2)
