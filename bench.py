@@ -189,42 +189,76 @@ def run_ours(args):
                 "ms_per_step": round(ms / K, 4), "impl": "ours", "config": {"workload": args.config}, "gpu_launches": launches,
                 "note": "value only (profiling run)"} if rank == 0 else None
 
-    # ---- roofline pass: event pairs around every tensor-core GEMM launch of a few more steps
+    # ---- roofline pass: event pairs around every kernel launch (C-ABI call) of a few more steps;
+    #      the tensor-core GEMM calls also record their shapes for the FLOP count
     prof = []
+    all_calls = []
     real_linear_call = _Linear.__call__
 
-    def timed_call(self, a, c, *pa, **kw):
+    def timed_linear(self, a, c, *pa, **kw):
+        m_dev = kw.get("m_dev")
+        prof.append((len(all_calls), self.weight.shape[0], self.weight.shape[1], a.shape[0] if m_dev is None else None))
+        real_linear_call(self, a, c, *pa, **kw)
+
+    def timed_call(name, *a):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        real_linear_call(self, a, c, *pa, **kw)
+        counting_call(name, *a)
         e1.record()
-        m_dev = kw.get("m_dev")
-        prof.append((e0, e1, self.weight.shape[0], self.weight.shape[1], a.shape[0] if m_dev is None else None))
+        all_calls.append((name, e0, e1))
 
     it = model.generate(rd.stats.Ledger(), prompt_dev, max_length, shape, sargs, special)
     for _ in range(3):
         next(it)
-    _Linear.__call__ = timed_call
+    _Linear.__call__ = timed_linear
+    _lib.call = timed_call
     flops = 0.0
     gemm_ms = 0.0
     n_gemm = 0
-    for _ in range(4):
+    by_kernel = {}
+    by_shape = {}
+    n_prof_steps = 4
+    for _ in range(n_prof_steps):
         prof.clear()
+        all_calls.clear()
         next(it)
         m_live = int(model.last_state.fp.row_start[-1].item())
-        for e0, e1, N, Kd, m_fixed in prof:
+        times = [(name, e0.elapsed_time(e1)) for name, e0, e1 in all_calls]
+        for name, ms_k in times:
+            agg = by_kernel.setdefault(name, [0, 0.0])
+            agg[0] += 1
+            agg[1] += ms_k
+        for idx, N, Kd, m_fixed in prof:
+            if idx >= len(times) or times[idx][0] != "rd_gemm_bf16_tc":
+                continue
             m = m_live if m_fixed is None else m_fixed
-            flops += 2.0 * m * N * Kd
-            gemm_ms += e0.elapsed_time(e1)
+            f = 2.0 * m * N * Kd
+            flops += f
+            gemm_ms += times[idx][1]
             n_gemm += 1
+            agg = by_shape.setdefault((N, Kd, m_fixed is None), [0, 0.0, 0.0])
+            agg[0] += 1
+            agg[1] += times[idx][1]
+            agg[2] += f
     _Linear.__call__ = real_linear_call
+    _lib.call = counting_call
     it.close()
     peaks = _peaks()
     ach = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    roofline = {"kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM, all verify + drafter projections)", "bound": "tensor", "achieved": round(ach, 2),
-                "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(ach / peaks["tflops"], 4), "traffic": None,
+    step_ms_prof = sum(v[1] for v in by_kernel.values()) / n_prof_steps
+    breakdown = {k: {"launches_per_step": v[0] / n_prof_steps, "ms_per_step": round(v[1] / n_prof_steps, 4),
+                     "share": round(v[1] / n_prof_steps / step_ms_prof, 4)} for k, v in sorted(by_kernel.items(), key=lambda kv: -kv[1][1])}
+    if args.verbose and rank == 0:
+        for k, v in breakdown.items():
+            print(f"[breakdown] {k:28s} {v['launches_per_step']:7.1f}/step {v['ms_per_step']:9.4f} ms {100 * v['share']:5.1f}%", file=sys.stderr)
+        for (N, Kd, dyn), v in sorted(by_shape.items(), key=lambda kv: -kv[1][1]):
+            print(f"[gemm] N={N:6d} K={Kd:6d} {'verify' if dyn else 'drafter'} n={v[0] // n_prof_steps:3d}/step avg {1e3 * v[1] / v[0]:7.1f} us "
+                  f"{v[2] / (v[1] * 1e-3) / 1e12:7.1f} TFLOP/s", file=sys.stderr)
+    roofline = {"kernel": "gemm_tc_pair_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM, all verify + drafter projections)", "bound": "tensor",
+                "achieved": round(ach, 2), "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(ach / peaks["tflops"], 4), "traffic": None,
                 "launches_timed": n_gemm, "flops_per_launch_avg": flops / max(n_gemm, 1), "peak_source": peaks["source"],
-                "gemm_share_of_step": round(gemm_ms / 4 / (ms / K), 4) if ms > 0 else None}
+                "gemm_share_of_step": round(gemm_ms / n_prof_steps / (ms / K), 4) if ms > 0 else None,
+                "kernel_time_breakdown": breakdown}
 
     # ---- end to end through the public API from pinned host memory
     barrier()
@@ -374,6 +408,7 @@ def main():
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--value-only", action="store_true", help="skip the roofline, end-to-end and CPU passes (profiler runs)")
+    ap.add_argument("--verbose", action="store_true", help="print the per-kernel and per-GEMM-shape timing breakdown to stderr")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -34,157 +34,271 @@ __global__ void drafter_prepare_kernel(const T* __restrict__ embed, const int64_
 }
 
 // ---------------------------------------------------------------------------------------------
-// rd_vocab_topk: one block per row.
+// rd_vocab_topk: one block per row, the row is streamed twice from global memory (the second pass
+// hits L2) and never staged in shared memory.
+//
+//   1. every thread takes the maximum of its strided share of the row; the top_k-th largest of these
+//      512 thread maxima is a LOWER bound T0 of the row's top_k-th largest value (the thread maxima
+//      are distinct elements of the row), and their largest is the row maximum;
+//   2. second pass: the elements >= T0 (typically one or two hundred) are collected;
+//   3. the exact top_k threshold, the ties at it and the (value descending, id ascending) order come
+//      from ranking the candidates against each other;
+//   4. log-softmax over the warped row from the kept entries alone (masked entries share one value).
+// A row with more than kCandCap elements >= T0 (massive ties) takes the radix-select path, which
+// reads the row a few more times.
 constexpr int kTopkThreads = 512;
 constexpr int kKept = RD_TOPK_MAX_KEPT;
+constexpr int kCandCap = 2048;
 
 template <typename T>
-__global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
-    const T* __restrict__ logits, int64_t ld, int rows_max, const int32_t* __restrict__ rows_dev, int V, int top_k,
-    float mask_value, int subtract_max, float temperature, float* __restrict__ kept_val, int32_t* __restrict__ kept_idx,
-    int32_t* __restrict__ kept_cnt, float* __restrict__ masked_logp) {
-  const int row = blockIdx.x;
-  if (row >= rd::live_rows(rows_dev, rows_max)) return;
-  extern __shared__ float z[];  // [V]
-  __shared__ float red[kTopkThreads / 32];
-  __shared__ int hist[256];
-  __shared__ uint32_t sel_prefix;
-  __shared__ int sel_remaining;
-  __shared__ int n_gt, n_tie_total;
-  __shared__ int scan[kTopkThreads];
-  __shared__ float cv[kKept];
-  __shared__ int ci[kKept];
-  __shared__ float sv[kKept];
-  __shared__ int si[kKept];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const T* src = logits + (int64_t)row * ld;
+struct RowReader {
+  const T* src;
+  int V;
+  bool vec;  // 16-byte loads allowed
+  static constexpr int VEC = 16 / sizeof(T);
+  // calls f(value, index) for this thread's share of the row
+  template <typename F>
+  __device__ __forceinline__ void for_each(int tid, F f) const {
+    if (vec) {
+      const int nvec = V / VEC;
+      for (int i = tid; i < nvec; i += kTopkThreads) {
+        T e[VEC];
+        *reinterpret_cast<uint4*>(e) = reinterpret_cast<const uint4*>(src)[i];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) f(rd::Num<T>::to_f(e[j]), i * VEC + j);
+      }
+      for (int v = nvec * VEC + tid; v < V; v += kTopkThreads) f(rd::Num<T>::to_f(src[v]), v);
+    } else {
+      for (int v = tid; v < V; v += kTopkThreads) f(rd::Num<T>::to_f(src[v]), v);
+    }
+  }
+};
 
-  // 1. load, row max
-  float mx = -INFINITY;
-  for (int v = tid; v < V; v += kTopkThreads) {
-    float f = rd::Num<T>::to_f(src[v]);
-    z[v] = f;
-    mx = fmaxf(mx, f);
-  }
-  mx = rd::warp_max(mx);
-  if (lane == 0) red[warp] = mx;
-  __syncthreads();
-  mx = red[0];
-  for (int w = 1; w < kTopkThreads / 32; ++w) mx = fmaxf(mx, red[w]);
-  __syncthreads();
-  if (subtract_max) {
-    for (int v = tid; v < V; v += kTopkThreads) z[v] = z[v] - mx;
-    mx = 0.f;
-  }
+struct TopkShared {
+  float lmax[kTopkThreads];
+  float cval[kCandCap];
+  int cidx[kCandCap];
+  int hist[256];
+  int scan[kTopkThreads];
+  float sv[kKept];
+  int si[kKept];
+  float t0, mx, thr;
+  int ccount, gt, ties, n_gt_fallback;
+  uint32_t sel_prefix;
+  int sel_remaining;
+};
+
+// Radix-select path for rows whose candidate set does not fit: exact threshold by 8-bit digits over
+// the whole row (read from global memory), then entries above it and ties in index order.
+template <typename T>
+__device__ void topk_radix_path(const RowReader<T>& row, TopkShared& sh, int top_k, int tid, int lane) {
+  const int V = row.V;
   if (tid == 0) {
-    sel_prefix = 0;
-    sel_remaining = top_k < V ? top_k : V;
+    sh.sel_prefix = 0;
+    sh.sel_remaining = top_k < V ? top_k : V;
   }
   __syncthreads();
-
-  // 2. radix select of the top_k-th largest key, 8 bits per pass from the top.  bf16 inputs have
-  //    16 significant key bits unless the row maximum was subtracted (the difference is fp32).
-  const int n_pass = (sizeof(T) == 2 && !subtract_max) ? 2 : 4;
-  for (int pass = 0; pass < n_pass; ++pass) {
+  for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     const uint32_t hi_mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-    for (int i = tid; i < 256; i += kTopkThreads) hist[i] = 0;
+    for (int i = tid; i < 256; i += kTopkThreads) sh.hist[i] = 0;
     __syncthreads();
-    const uint32_t prefix = sel_prefix;
-    // logits crowd into a few exponent bins: aggregate equal digits inside the warp so that one
-    // lane per distinct digit does the shared-memory atomic
+    const uint32_t prefix = sh.sel_prefix;
     for (int v0 = 0; v0 < V; v0 += kTopkThreads) {
       const int v = v0 + tid;
       uint32_t key = 0;
       bool in = false;
       if (v < V) {
-        key = rd::float_key(z[v]);
+        key = rd::float_key(rd::Num<T>::to_f(row.src[v]));
         in = (key & hi_mask) == prefix;
       }
       const uint32_t digit = in ? ((key >> shift) & 255u) : 256u;
       const uint32_t peers = __match_any_sync(0xffffffffu, digit);
-      if (in && lane == (__ffs(peers) - 1)) atomicAdd(&hist[digit], __popc(peers));
+      if (in && lane == (__ffs(peers) - 1)) atomicAdd(&sh.hist[digit], __popc(peers));
     }
     __syncthreads();
     if (tid == 0) {
-      int rem = sel_remaining, d = 255;
+      int rem = sh.sel_remaining, d = 255;
       for (; d > 0; --d) {
-        if (hist[d] >= rem) break;
-        rem -= hist[d];
+        if (sh.hist[d] >= rem) break;
+        rem -= sh.hist[d];
       }
-      sel_prefix = prefix | ((uint32_t)d << shift);
-      sel_remaining = rem;
+      sh.sel_prefix = prefix | ((uint32_t)d << shift);
+      sh.sel_remaining = rem;
     }
     __syncthreads();
   }
-  const uint32_t thr_key = sel_prefix;  // key of the top_k-th largest value
-  if (tid == 0) {
-    n_gt = 0;
-    n_tie_total = 0;
-  }
+  const uint32_t thr_key = sh.sel_prefix;
+  if (tid == 0) sh.n_gt_fallback = 0;
   __syncthreads();
-
-  // 3. entries strictly above the threshold (fewer than top_k of them), any order
+  // entries strictly above the threshold (fewer than top_k), any order, into cval/cidx
   for (int v = tid; v < V; v += kTopkThreads) {
-    if (rd::float_key(z[v]) > thr_key) {
-      int s = atomicAdd(&n_gt, 1);
+    const float f = rd::Num<T>::to_f(row.src[v]);
+    if (rd::float_key(f) > thr_key) {
+      const int s = atomicAdd(&sh.n_gt_fallback, 1);
       if (s < kKept) {
-        cv[s] = z[v];
-        ci[s] = v;
+        sh.cval[s] = f;
+        sh.cidx[s] = v;
       }
     }
   }
-  // 4. ties at the threshold, in ascending index order, while capacity lasts
+  // ties in ascending index order while capacity lasts (blocked assignment + scan)
   const int chunk = (V + kTopkThreads - 1) / kTopkThreads;
   const int v0 = tid * chunk, v1 = min(V, v0 + chunk);
   int my_ties = 0;
-  for (int v = v0; v < v1; ++v) my_ties += (rd::float_key(z[v]) == thr_key);
-  scan[tid] = my_ties;
+  float thr_val = 0.f;
+  for (int v = v0; v < v1; ++v) {
+    const float f = rd::Num<T>::to_f(row.src[v]);
+    if (rd::float_key(f) == thr_key) {
+      ++my_ties;
+      thr_val = f;
+    }
+  }
+  sh.scan[tid] = my_ties;
   __syncthreads();
   for (int o = 1; o < kTopkThreads; o <<= 1) {
-    int add = tid >= o ? scan[tid - o] : 0;
+    const int add = tid >= o ? sh.scan[tid - o] : 0;
     __syncthreads();
-    scan[tid] += add;
+    sh.scan[tid] += add;
     __syncthreads();
   }
-  const int gt = min(n_gt, kKept);
-  int pos = gt + scan[tid] - my_ties;
+  const int gt = min(sh.n_gt_fallback, kKept);
+  int pos = gt + sh.scan[tid] - my_ties;
   for (int v = v0; v < v1; ++v) {
-    if (rd::float_key(z[v]) == thr_key) {
+    const float f = rd::Num<T>::to_f(row.src[v]);
+    if (rd::float_key(f) == thr_key) {
       if (pos < kKept) {
-        cv[pos] = z[v];
-        ci[pos] = v;
+        sh.cval[pos] = f;
+        sh.cidx[pos] = v;
       }
       ++pos;
     }
   }
-  if (tid == kTopkThreads - 1) n_tie_total = scan[tid];
-  __syncthreads();
-  const int ties = n_tie_total;
-  const int cnt = min(kKept, gt + ties);
-
-  // 5. order the kept list by (value descending, id ascending)
-  if (tid < cnt) {
-    const float mv = cv[tid];
-    const int mi = ci[tid];
-    int rank = 0;
-    for (int o = 0; o < cnt; ++o) rank += (cv[o] > mv) || (cv[o] == mv && ci[o] < mi);
-    sv[rank] = mv;
-    si[rank] = mi;
+  if (my_ties > 0) sh.thr = thr_val;
+  if (tid == kTopkThreads - 1) {
+    sh.gt = gt;
+    sh.ties = sh.scan[tid];
+    sh.ccount = min(kKept, gt + sh.scan[tid]);
   }
   __syncthreads();
+}
 
-  // 6. log-softmax over the warped row: kept entries, ties that did not fit, and masked entries
+template <typename T>
+__global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
+    const T* __restrict__ logits, int64_t ld, int rows_max, const int32_t* __restrict__ rows_dev, int V, int top_k,
+    float mask_value, int subtract_max, float temperature, int vec_ok, float* __restrict__ kept_val,
+    int32_t* __restrict__ kept_idx, int32_t* __restrict__ kept_cnt, float* __restrict__ masked_logp) {
+  const int row_id = blockIdx.x;
+  if (row_id >= rd::live_rows(rows_dev, rows_max)) return;
+  __shared__ TopkShared sh;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  RowReader<T> row{logits + (int64_t)row_id * ld, V, vec_ok != 0};
+  const int K = top_k < V ? top_k : V;
+
+  // 1. thread maxima -> lower bound T0 of the K-th largest value, and the row maximum
+  float lm = -INFINITY;
+  row.for_each(tid, [&](float f, int) { lm = fmaxf(lm, f); });
+  sh.lmax[tid] = lm;
+  if (tid == 0) {
+    sh.ccount = 0;
+    sh.gt = 0;
+    sh.ties = 0;
+    sh.t0 = -INFINITY;
+  }
+  __syncthreads();
+  {
+    int rank = 0;
+    for (int o = 0; o < kTopkThreads; ++o) {
+      const float v = sh.lmax[o];
+      rank += (v > lm) || (v == lm && o < tid);
+    }
+    if (rank == 0) sh.mx = lm;
+    if (rank == K - 1 && lm > -INFINITY) sh.t0 = lm;  // stays -inf when fewer than K threads hold elements
+  }
+  __syncthreads();
+  const float t0 = sh.t0, mx = sh.mx;
+
+  // 2. candidates
+  row.for_each(tid, [&](float f, int v) {
+    if (f >= t0) {
+      const int s = atomicAdd(&sh.ccount, 1);
+      if (s < kCandCap) {
+        sh.cval[s] = f;
+        sh.cidx[s] = v;
+      }
+    }
+  });
+  __syncthreads();
+  const int n_cand = sh.ccount;
+  int cnt;
+  if (n_cand > kCandCap) {
+    __syncthreads();
+    topk_radix_path(row, sh, K, tid, lane);
+    cnt = sh.ccount;
+    // order the (at most kKept) survivors
+    if (tid < cnt) {
+      const float mv = sh.cval[tid];
+      const int mi = sh.cidx[tid];
+      int rank = 0;
+      for (int o = 0; o < cnt; ++o) rank += (sh.cval[o] > mv) || (sh.cval[o] == mv && sh.cidx[o] < mi);
+      sh.sv[rank] = mv;
+      sh.si[rank] = mi;
+    }
+    __syncthreads();
+  } else {
+    // 3. rank the candidates: unique ranks in (value descending, id ascending) order
+    int my_rank[kCandCap / kTopkThreads];
+#pragma unroll
+    for (int c = 0; c < kCandCap / kTopkThreads; ++c) {
+      const int i = c * kTopkThreads + tid;
+      my_rank[c] = -1;
+      if (i < n_cand) {
+        const float mv = sh.cval[i];
+        const int mi = sh.cidx[i];
+        int rank = 0;
+        for (int o = 0; o < n_cand; ++o) {
+          const float ov = sh.cval[o];
+          rank += (ov > mv) || (ov == mv && sh.cidx[o] < mi);
+        }
+        my_rank[c] = rank;
+        if (rank == K - 1) sh.thr = mv;
+      }
+    }
+    __syncthreads();
+    const float thr = sh.thr;
+#pragma unroll
+    for (int c = 0; c < kCandCap / kTopkThreads; ++c) {
+      const int i = c * kTopkThreads + tid;
+      if (i < n_cand) {
+        const float mv = sh.cval[i];
+        if (mv > thr) atomicAdd(&sh.gt, 1);
+        if (mv == thr) atomicAdd(&sh.ties, 1);
+      }
+    }
+    __syncthreads();
+    cnt = min(kKept, sh.gt + sh.ties);
+#pragma unroll
+    for (int c = 0; c < kCandCap / kTopkThreads; ++c) {
+      const int i = c * kTopkThreads + tid;
+      if (i < n_cand && my_rank[c] >= 0 && my_rank[c] < cnt) {
+        sh.sv[my_rank[c]] = sh.cval[i];
+        sh.si[my_rank[c]] = sh.cidx[i];
+      }
+    }
+    __syncthreads();
+  }
+
+  // 4. log-softmax over the warped row: kept entries, ties that did not fit, and masked entries
   if (warp == 0) {
-    const float inv_t = 1.0f;  // the division below keeps the reference's rounding
-    (void)inv_t;
-    const float top = sv[0] / temperature;
+    const int gt = sh.gt, ties = sh.ties;
+    const float shift = subtract_max ? mx : 0.f;
+    const float top = (sh.sv[0] - shift) / temperature;
     const float masked_s = mask_value / temperature;
     const float m = fmaxf(top, masked_s);
     float acc = 0.f;
-    for (int o = lane; o < cnt; o += 32) acc += expf(sv[o] / temperature - m);
+    for (int o = lane; o < cnt; o += 32) acc += expf((sh.sv[o] - shift) / temperature - m);
     acc = rd::warp_sum(acc);
-    const float thr_val = sv[cnt - 1];
+    const float thr_val = sh.sv[cnt - 1] - shift;
     const int dropped = gt + ties - cnt;
     const int n_masked = V - gt - ties;
     acc += (float)dropped * expf(thr_val / temperature - m);
@@ -192,12 +306,12 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
     const float lse = m + logf(acc);
     for (int o = lane; o < kKept; o += 32) {
       const bool live = o < cnt;
-      kept_val[(int64_t)row * kKept + o] = live ? (sv[o] / temperature - lse) : -INFINITY;
-      kept_idx[(int64_t)row * kKept + o] = live ? si[o] : -1;
+      kept_val[(int64_t)row_id * kKept + o] = live ? ((sh.sv[o] - shift) / temperature - lse) : -INFINITY;
+      kept_idx[(int64_t)row_id * kKept + o] = live ? sh.si[o] : -1;
     }
     if (lane == 0) {
-      kept_cnt[row] = cnt;
-      masked_logp[row] = masked_s - lse;
+      kept_cnt[row_id] = cnt;
+      masked_logp[row_id] = masked_s - lse;
     }
   }
 }
@@ -362,20 +476,17 @@ extern "C" int rd_vocab_topk(int logits_dtype, const void* logits, int64_t ld, i
   RD_REQUIRE(logits && kept_val && kept_idx && kept_cnt && masked_logp, RD_ERR_ARG);
   RD_REQUIRE(rows_max >= 1 && V >= 1 && top_k >= 1 && top_k <= RD_TOPK_MAX_KEPT && ld >= V, RD_ERR_SIZE);
   RD_REQUIRE(temperature > 0.f, RD_ERR_ARG);
-  const size_t smem = (size_t)V * sizeof(float);
-  RD_REQUIRE(smem <= 200 * 1024, RD_ERR_SIZE);
   cudaStream_t s = (cudaStream_t)stream;
   if (logits_dtype == RD_F32) {
-    auto kern = vocab_topk_kernel<float>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<rows_max, kTopkThreads, smem, s>>>((const float*)logits, ld, rows_max, rows_dev, V, top_k, mask_value,
-                                              subtract_max, temperature, kept_val, kept_idx, kept_cnt, masked_logp);
+    const int vec_ok = ((uintptr_t)logits % 16 == 0) && ((ld * 4) % 16 == 0);
+    vocab_topk_kernel<float><<<rows_max, kTopkThreads, 0, s>>>((const float*)logits, ld, rows_max, rows_dev, V, top_k, mask_value,
+                                                               subtract_max, temperature, vec_ok, kept_val, kept_idx, kept_cnt,
+                                                               masked_logp);
   } else if (logits_dtype == RD_BF16) {
-    auto kern = vocab_topk_kernel<__nv_bfloat16>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<rows_max, kTopkThreads, smem, s>>>((const __nv_bfloat16*)logits, ld, rows_max, rows_dev, V, top_k,
-                                              mask_value, subtract_max, temperature, kept_val, kept_idx, kept_cnt,
-                                              masked_logp);
+    const int vec_ok = ((uintptr_t)logits % 16 == 0) && ((ld * 2) % 16 == 0);
+    vocab_topk_kernel<__nv_bfloat16><<<rows_max, kTopkThreads, 0, s>>>((const __nv_bfloat16*)logits, ld, rows_max, rows_dev, V,
+                                                                       top_k, mask_value, subtract_max, temperature, vec_ok,
+                                                                       kept_val, kept_idx, kept_cnt, masked_logp);
   } else {
     return RD_ERR_DTYPE;
   }

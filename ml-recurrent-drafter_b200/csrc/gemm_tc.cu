@@ -107,16 +107,27 @@ __device__ __forceinline__ uint32_t umma_instr_desc(int n) {
 }
 
 // Token chunking shared by all roles: n_chunks equal chunks of `chunk` tokens (a multiple of 16).
+// The fewest chunks that respect the 256-token MMA limit are used unless that leaves compute units
+// (CTAs or CTA pairs) idle: a GEMM with few weight tiles (N = 4096) then cuts the tokens finer so
+// that about one tile exists per unit.
 struct Chunking {
   int n_chunks, chunk;
 };
-__device__ __forceinline__ Chunking make_chunking(int M) {
+__device__ __forceinline__ Chunking make_chunking(int M, int w_units, int avail_units) {
   Chunking c;
   c.n_chunks = (M + kMaxChunk - 1) / kMaxChunk;
   if (c.n_chunks < 1) c.n_chunks = 1;
+  if (w_units * c.n_chunks < avail_units) {
+    int n = avail_units / w_units;             // tiles <= units: a single, fuller wave
+    const int n_cap = (M + 63) / 64;           // keep chunks of at least ~64 tokens
+    if (n > n_cap) n = n_cap;
+    if (n > c.n_chunks) c.n_chunks = n;
+  }
   const int per = (M + c.n_chunks - 1) / c.n_chunks;
   c.chunk = ((per + 15) / 16) * 16;
   if (c.chunk < 16) c.chunk = 16;
+  c.n_chunks = (M + c.chunk - 1) / c.chunk;    // rounding up to 16 may have emptied the last chunk
+  if (c.n_chunks < 1) c.n_chunks = 1;
   return c;
 }
 // MMA N of chunk ci: its live tokens rounded up to 16
@@ -324,8 +335,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = rd::live_rows(m_dev, m_max);
-  const Chunking ch = make_chunking(M);
   const int w_tiles = (N + BM - 1) / BM;
+  const Chunking ch = make_chunking(M, w_tiles, gridDim.x);
   const int total_tiles = M > 0 ? w_tiles * ch.n_chunks : 0;
   const int k_blocks = K / BK;
 
@@ -571,8 +582,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int M = rd::live_rows(m_dev, m_max);
-  const Chunking ch = make_chunking(M);
   const int w_pairs = (N + 2 * BM - 1) / (2 * BM);
+  const Chunking ch = make_chunking(M, w_pairs, n_pairs);
   const int total_tiles = M > 0 ? w_pairs * ch.n_chunks : 0;
   const int k_blocks = K / BK;
 
@@ -797,7 +808,8 @@ int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const int chunks = (p->m_max + kMaxChunk - 1) / kMaxChunk;
+  // upper bound of the tile count with the finest chunking the kernel may choose (64 tokens)
+  const int chunks = (p->m_max + 63) / 64;
   if (p->N >= 2 * BM && g_use_pairs) {
     // CTA pairs: one pair per 256 weight rows x token chunk
     const int tiles = chunks * ((p->N + 2 * BM - 1) / (2 * BM));

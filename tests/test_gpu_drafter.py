@@ -94,3 +94,28 @@ def test_beam_search_bf16_tolerance():
     got4 = got4.cpu().numpy()
     same = sum(tuple(r) in {tuple(x) for x in want4[b]} for b in range(B) for r in got4[b])
     assert same >= B * W // 2, same
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_vocab_topk_massive_ties(dtype):
+    """Rows where thousands of entries tie at the top-k threshold (the radix-select path): the list
+    holds the entries above the threshold, then ties by ascending id up to the capacity; the
+    normaliser still counts every tie."""
+    import recurrent_drafting as rd
+
+    md = rd.modeling_drafter
+    V, rows = 6000, 3
+    logits = np.zeros((rows, V), dtype=np.float32)
+    logits[0, [5, 99, 4000]] = [3.0, 2.0, 1.0]
+    logits[1, :] = -1.5
+    logits[2, 10:3000] = 1.0
+    tl = t(logits).to(dtype)
+    sp = md.vocab_topk(tl, md.new_sparse(rows, "cuda"), subtract_max=True)
+    val, idx, cnt, masked = (x.cpu().numpy() for x in (sp.val, sp.idx, sp.cnt, sp.masked))
+    want = odr.log_softmax(odr.warp_logits(odr.maintain_logits(logits)))
+    assert cnt.tolist() == [64, 64, 64]
+    assert idx[0, :3].tolist() == [5, 99, 4000] and idx[0, 3:64].tolist() == [i for i in range(64) if i != 5][:61]
+    assert idx[1].tolist() == list(range(64))
+    assert idx[2].tolist() == list(range(10, 74))
+    for r in range(rows):
+        np.testing.assert_allclose(val[r], want[r, idx[r]], rtol=1e-5, atol=2e-5)
