@@ -43,6 +43,8 @@ CONFIGS = {
     "c4": (dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=40, num_hidden_layers=40,
                 intermediate_size=13824, vocab_size=32000), 2, 8, 32, 5, 1024, 1024, "bf16", True, 1.0),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum of the four GEMMs of one verify layer (down, QKV, o, gate/up), mean per launch
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = int((113.2 + 3.8 + 109.4 + 4.7 + 45.8 + 0.1 + 191.5 + 12.5) / 4 * 1e6)
 METRIC = "generated tokens/sec (ReDrafter decode, 7B-arch bw45xbl5 bs8 per GPU)"
 
 
@@ -255,7 +257,9 @@ def run_ours(args):
             print(f"[gemm] N={N:6d} K={Kd:6d} {'verify' if dyn else 'drafter'} n={v[0] // n_prof_steps:3d}/step avg {1e3 * v[1] / v[0]:7.1f} us "
                   f"{v[2] / (v[1] * 1e-3) / 1e12:7.1f} TFLOP/s", file=sys.stderr)
     roofline = {"kernel": "gemm_tc_pair_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM, all verify + drafter projections)", "bound": "tensor",
-                "achieved": round(ach, 2), "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(ach / peaks["tflops"], 4), "traffic": None,
+                "achieved": round(ach, 2), "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(ach / peaks["tflops"], 4), "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH,
+                "traffic_note": "DRAM read+write per launch, mean over the verify layer's four GEMMs, from the ncu capture in "
+                                "profiles/gemm_tc_pair_kernel_c2_verify.md (c2 shapes on 4 layers)",
                 "launches_timed": n_gemm, "flops_per_launch_avg": flops / max(n_gemm, 1), "peak_source": peaks["source"],
                 "gemm_share_of_step": round(gemm_ms / n_prof_steps / (ms / K), 4) if ms > 0 else None,
                 "kernel_time_breakdown": breakdown}
@@ -279,17 +283,14 @@ def run_ours(args):
     e2e_ms = e0.elapsed_time(e1)
     it.close()
 
-    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
-    tok = torch.tensor([float(tokens), float(e2e_tokens), float(accepted)], dtype=torch.float64, device=dev)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(tok, op=dist.ReduceOp.SUM)
-        # the one collective of the path: gather of the final tokens to rank 0 (off the timed region)
-        final = sink[:, : Lp + 8].to(dev)
-        gathered = [torch.empty_like(final) for _ in range(world)] if rank == 0 else None
-        dist.gather(final, gathered, dst=0)
-    ms, e2e_ms = t.tolist()
-    tokens, e2e_tokens, accepted = tok.tolist()
+        from recurrent_drafting import replicas
+
+        e2e_ms, e2e_tokens, _ = replicas.reduce_stats(e2e_ms, float(e2e_tokens), 0.0, dev)
+        ms, tokens, accepted = replicas.reduce_stats(ms, float(tokens), float(accepted), dev)
+        # the one collective of the path: gather of the generated tokens on rank 0 (outside the timed regions)
+        gathered = replicas.gather_tokens(sink[:, : Lp + K].to(dev), 0, dst=0)
+        assert rank != 0 or (len(gathered) == world and all(g.shape[0] == B for g in gathered))
     line = None
     if rank == 0:
         line = {

@@ -11,6 +11,7 @@ from . import (  # noqa: F401
     modeling_drafter,
     modeling_llama,
     recurrent_drafting,
+    replicas,
     rng,
     stats,
     tree_attention,
