@@ -1,8 +1,10 @@
 // Tree-masked flash attention on the 5th-generation tensor cores (head_dim 128, bf16).
 //
 // One CTA serves 128 queries of one (batch row, head): normally every packed tree token of the row.
-//   warp 0      TMA producer: the Q tile once, then K and V tiles of 64 keys (two 64-column boxes
-//               each, 128-byte swizzle, no multicast) into a two-stage ring;
+//   warp 0      TMA producers: lane 0 loads the Q tile once and then the K tiles of 64 keys, lane 1
+//               the V tiles (two 64-column boxes each, 128-byte swizzle, no multicast), each into
+//               its own two-stage ring: a K stage is released as soon as QK^T of its tile is done,
+//               a V stage after PV, so the K loads run well ahead of the V loads;
 //   warp 1      MMA issuer (one elected thread):
 //                 S = Q K^T   tcgen05.mma, A = Q and B = K from shared memory (both K-major),
 //                             accumulator S[128 x 64] in TMEM;
@@ -13,8 +15,9 @@
 //               sum in the exp2 domain, P written back to TMEM with tcgen05.st.  O accumulates in
 //               TMEM across tiles; a warp rescales its O rows (tcgen05.ld / st) only on the tiles
 //               where one of its rows' running max actually moved.
-// QK of tile t+1 overlaps the softmax and PV of tile t; two CTAs fit on an SM (96 KB of shared
-// memory, 256 TMEM columns each) and overlap each other's latencies.
+// QK of tile t+1 overlaps the softmax and PV of tile t; P is double-buffered in TMEM so that the
+// softmax of tile t never waits for PV of tile t-1; two CTAs fit on an SM (96 KB of shared memory,
+// 256 TMEM columns each) and overlap each other's latencies.
 //
 // Every mbarrier wait is bounded; on give-up the kernel records a code in *status, stops issuing,
 // lets outstanding bulk copies land, frees its TMEM and returns.
@@ -38,7 +41,7 @@ constexpr int kMaskBytes = BMQ * kMaxMaskWords * 4;  // the tile's bitmask rows
 constexpr int kSmemBytes = kQBytes + kStages * kKVStage + kMaskBytes + 1024 + 256;
 // TMEM columns
 constexpr uint32_t kColS = 0;     // S: 64 fp32 columns
-constexpr uint32_t kColP = 64;    // P: 64 bf16 = 32 columns
+constexpr uint32_t kColP = 64;    // P: two buffers of 64 bf16 = 32 columns each
 constexpr uint32_t kColO = 128;   // O: 128 fp32 columns, accumulated over the tiles
 constexpr uint32_t kTmemCols = 256;
 
@@ -169,13 +172,15 @@ __global__ void __launch_bounds__(kThreads, 2)
   uint32_t* sMask = reinterpret_cast<uint32_t*>(smem + kQBytes + kStages * kKVStage);  // [128][mask_words]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kQBytes + kStages * kKVStage + kMaskBytes);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* s_empty = bars + 6;
-  uint64_t* p_full = bars + 7;
-  uint64_t* o_full = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;
+  uint64_t* s_empty = bars + 10;
+  uint64_t* p_full = bars + 11;
+  uint64_t* o_full = bars + 12;   // [2]: PV of even / odd tiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -188,13 +193,15 @@ __global__ void __launch_bounds__(kThreads, 2)
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&o_full[s], 1);
     }
     mbar_init(s_full, 1);
     mbar_init(s_empty, 4);
     mbar_init(p_full, 4);
-    mbar_init(o_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -209,26 +216,30 @@ __global__ void __launch_bounds__(kThreads, 2)
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      mbar_expect_tx(q_full, kQBytes);
-      tma_load_2d(sQ, &map_q, q_full, h * HD, rs + q0);
-      tma_load_2d(sQ + BMQ * 128, &map_q, q_full, h * HD + 64, rs + q0);
+    // ---------------- TMA producers: lane 0 = Q and K ring, lane 1 = V ring ----------------
+    if (lane < 2) {
+      const bool is_k = lane == 0;
+      if (is_k) {
+        mbar_expect_tx(q_full, kQBytes);
+        tma_load_2d(sQ, &map_q, q_full, h * HD, rs + q0);
+        tma_load_2d(sQ + BMQ * 128, &map_q, q_full, h * HD + 64, rs + q0);
+      }
+      uint64_t* full = is_k ? k_full : v_full;
+      uint64_t* empty = is_k ? k_empty : v_empty;
+      const CUtensorMap* map = is_k ? &map_k : &map_v;
       bool ok = true;
       for (int t = 0; ok && t < n_tiles; ++t) {
         const int s = t & 1;
         const uint32_t phase = (t >> 1) & 1;
-        if (!mbar_wait(&kv_empty[s], phase ^ 1, abort_flag)) {
+        if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) {
           ok = false;
           break;
         }
-        uint8_t* dst = sKV + s * kKVStage;
-        mbar_expect_tx(&kv_full[s], kKVStage);
+        uint8_t* dst = sKV + s * kKVStage + (is_k ? 0 : 2 * kSubTile);
+        mbar_expect_tx(&full[s], 2 * kSubTile);
         const int row = kv_row0 + t * BNK;
-        tma_load_2d(dst, &map_k, &kv_full[s], 0, row);
-        tma_load_2d(dst + kSubTile, &map_k, &kv_full[s], 64, row);
-        tma_load_2d(dst + 2 * kSubTile, &map_v, &kv_full[s], 0, row);
-        tma_load_2d(dst + 3 * kSubTile, &map_v, &kv_full[s], 64, row);
+        tma_load_2d(dst, map, &full[s], 0, row);
+        tma_load_2d(dst + kSubTile, map, &full[s], 64, row);
       }
       if (!ok) {
         if (atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 21);
@@ -251,9 +262,10 @@ __global__ void __launch_bounds__(kThreads, 2)
           umma_ss(tS, da, db, idesc_qk, kd != 0);
         }
         umma_commit(s_full);
+        umma_commit(&k_empty[t & 1]);  // the K stage is free once this product is done
       };
       if (ok && n_tiles > 0) {
-        ok = mbar_wait(&kv_full[0], 0, abort_flag);
+        ok = mbar_wait(&k_full[0], 0, abort_flag);
         if (ok) {
           tc_fence_after();
           issue_qk(0);
@@ -262,15 +274,15 @@ __global__ void __launch_bounds__(kThreads, 2)
       for (int t = 0; ok && t < n_tiles; ++t) {
         if (t + 1 < n_tiles) {
           // S of tile t has been read by the softmax threads -> QK of tile t+1 may overwrite it
-          if (!mbar_wait(&kv_full[(t + 1) & 1], ((t + 1) >> 1) & 1, abort_flag) || !mbar_wait(s_empty, t & 1, abort_flag)) {
+          if (!mbar_wait(&k_full[(t + 1) & 1], ((t + 1) >> 1) & 1, abort_flag) || !mbar_wait(s_empty, t & 1, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
           issue_qk(t + 1);
         }
-        // P of tile t is in TMEM (and O has been rescaled where needed)
-        if (!mbar_wait(p_full, t & 1, abort_flag)) {
+        // P of tile t is in TMEM (and O has been rescaled where needed); V of tile t has landed
+        if (!mbar_wait(p_full, t & 1, abort_flag) || !mbar_wait(&v_full[t & 1], (t >> 1) & 1, abort_flag)) {
           ok = false;
           break;
         }
@@ -281,10 +293,10 @@ __global__ void __launch_bounds__(kThreads, 2)
           // V: keys are the K dimension (rows of 128 bytes), head_dim the MN dimension: two 64-wide
           // halves kSubTile bytes apart, 8-key groups 1024 bytes apart; 16 keys per MMA = 2048 bytes
           const uint64_t dv = desc_mn_major(smem_u32(sV + ks * 2048), kSubTile, 1024);
-          umma_ts(tO, tP + ks * 8, dv, idesc_pv, (t | ks) != 0);
+          umma_ts(tO, tP + (t & 1) * 32 + ks * 8, dv, idesc_pv, (t | ks) != 0);
         }
-        umma_commit(o_full);
-        umma_commit(&kv_empty[t & 1]);
+        umma_commit(&o_full[t & 1]);
+        umma_commit(&v_empty[t & 1]);
       }
       if (!ok && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 22);
     }
@@ -313,35 +325,40 @@ __global__ void __launch_bounds__(kThreads, 2)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty);
-      // scale, visibility, running max
+      // visibility of the tile's 64 keys for this row as one 64-bit word
       const int j0 = t * BNK;
-      float mx = -INFINITY;
-      if (j0 + BNK <= base && j0 + BNK <= kv_end) {
-        // the whole tile lies in the cached prefix: every key is visible
-#pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const float v = __uint_as_float(sb[i]) * scale_log2;
-          sb[i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+      uint64_t vis;
+      if (j0 + BNK <= base) {
+        vis = ~0ull;  // the whole tile lies in the cached prefix
       } else {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const int j = j0 + i;
-          float v = __uint_as_float(sb[i]) * scale_log2;
-          bool vis;
-          if (j >= kv_end)
-            vis = false;
-          else if (j < base)
-            vis = true;
-          else {
-            const int jn = j - base;
-            vis = (mode == RD_ATTN_CAUSAL) ? (jn <= qi) : ((my_mask[jn >> 5] >> (jn & 31)) & 1u);
-          }
-          v = vis ? v : -INFINITY;
-          sb[i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+        const int off = j0 - base;  // index of the tile's first key among the new tokens (may be negative)
+        uint64_t nb;                // visibility of new tokens [max(off,0), ...) aligned to bit max(-off,0)
+        const int first = off > 0 ? off : 0;
+        if (mode == RD_ATTN_CAUSAL) {
+          // new token jn is visible iff jn <= qi
+          const int n_vis = qi - first + 1;
+          nb = n_vis >= 64 ? ~0ull : (n_vis <= 0 ? 0ull : ((1ull << n_vis) - 1ull));
+        } else {
+          const int w = first >> 5, sh = first & 31;
+          const uint64_t lo = w < mask_words ? my_mask[w] : 0u;
+          const uint64_t mid = w + 1 < mask_words ? my_mask[w + 1] : 0u;
+          const uint64_t hi = w + 2 < mask_words ? my_mask[w + 2] : 0u;
+          nb = ((lo | (mid << 32)) >> sh) | (sh ? (hi << (64 - sh)) : 0ull);
         }
+        vis = off >= 0 ? nb : ((nb << (-off)) | ((1ull << (-off)) - 1ull));
+      }
+      if (j0 + BNK > kv_end) {
+        const int n_in = kv_end - j0;  // 1..63 keys of the tile exist
+        vis &= (n_in <= 0) ? 0ull : ((1ull << n_in) - 1ull);
+      }
+      // scale, mask, running max
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float v = __uint_as_float(sb[i]) * scale_log2;
+        v = ((vis >> i) & 1ull) ? v : -INFINITY;
+        sb[i] = __float_as_uint(v);
+        mx = fmaxf(mx, v);
       }
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -358,31 +375,34 @@ __global__ void __launch_bounds__(kThreads, 2)
         pb[i] = pack_bf16(p0, p1);
       }
       l_run = l_run * alpha + rowsum;
-      if (t > 0) {
-        // PV of tile t-1 must be complete before its P is overwritten or O is touched
-        if (!mbar_wait(o_full, (t - 1) & 1, abort_flag)) {
+      // P buffer t&1 was last read by PV of tile t-2: wait for that product (long done)
+      if (t >= 2 && !mbar_wait(&o_full[t & 1], ((t - 2) >> 1) & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      if (__any_sync(0xffffffffu, moved)) {
+        // O must be quiescent while it is rescaled: PV of tile t-1 has to be complete
+        if (!mbar_wait(&o_full[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, moved)) {
-          const float a = moved ? alpha : 1.0f;
+        const float a = moved ? alpha : 1.0f;
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
-            uint32_t ob[32];
-            tmem_ld32(lane_addr + kColO + c * 32, ob);
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t ob[32];
+          tmem_ld32(lane_addr + kColO + c * 32, ob);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ob[i] = __float_as_uint(__uint_as_float(ob[i]) * a);
-            tmem_st32(lane_addr + kColO + c * 32, ob);
-          }
+          for (int i = 0; i < 32; ++i) ob[i] = __float_as_uint(__uint_as_float(ob[i]) * a);
+          tmem_st32(lane_addr + kColO + c * 32, ob);
         }
       }
-      tmem_st32(lane_addr + kColP, pb);
+      tmem_st32(lane_addr + kColP + (t & 1) * 32, pb);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(o_full, (n_tiles - 1) & 1, abort_flag);
+    if (ok && n_tiles > 0) ok = mbar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
