@@ -1,9 +1,9 @@
 // Tree-masked flash attention on the 5th-generation tensor cores (head_dim 128, bf16).
 //
 // One CTA serves 128 queries of one (batch row, head): normally every packed tree token of the row.
-//   warp 0      TMA producers: lane 0 loads the Q tile once and then the K tiles of 64 keys, lane 1
-//               the V tiles (two 64-column boxes each, 128-byte swizzle, no multicast), each into
-//               its own two-stage ring: a K stage is released as soon as QK^T of its tile is done,
+//   warps 0, 6  TMA producers (one elected lane each): warp 0 loads the Q tile once and then the K
+//               tiles of 64 keys, warp 6 the V tiles (two 64-column boxes each, 128-byte swizzle, no
+//               multicast), each into its own two-stage ring: a K stage is released as soon as QK^T of its tile is done,
 //               a V stage after PV, so the K loads run well ahead of the V loads;
 //   warp 1      MMA issuer (one elected thread):
 //                 S = Q K^T   tcgen05.mma, A = Q and B = K from shared memory (both K-major),
@@ -30,7 +30,7 @@ namespace {
 constexpr int HD = 128;
 constexpr int BMQ = 128;  // queries per CTA
 constexpr int BNK = 64;   // keys per tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int kSubTile = 64 * 128;            // bytes of a [64 rows x 64 bf16] box = 8 KB
 constexpr int kQBytes = BMQ * HD * 2;         // 32 KB: two [128 x 64] boxes
@@ -40,6 +40,7 @@ constexpr int kMaxMaskWords = 16;
 constexpr int kMaskBytes = BMQ * kMaxMaskWords * 4;  // the tile's bitmask rows
 constexpr int kSmemBytes = kQBytes + kStages * kKVStage + kMaskBytes + 1024 + 256;
 // TMEM columns
+constexpr float kMaxSlack = 6.0f;  // log2 units the tile max may exceed the running max without moving it
 constexpr uint32_t kColS = 0;     // S: 64 fp32 columns
 constexpr uint32_t kColP = 64;    // P: two buffers of 64 bf16 = 32 columns each
 constexpr uint32_t kColO = 128;   // O: 128 fp32 columns, accumulated over the tiles
@@ -122,6 +123,11 @@ __device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b,
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -215,10 +221,10 @@ __global__ void __launch_bounds__(kThreads, 2)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    // ---------------- TMA producers: lane 0 = Q and K ring, lane 1 = V ring ----------------
-    if (lane < 2) {
-      const bool is_k = lane == 0;
+  if (warp == 0 || warp == 6) {
+    // ---------------- TMA producers: warp 0 = Q and the K ring, warp 6 = the V ring ----------------
+    if (lane == 0) {
+      const bool is_k = warp == 0;
       if (is_k) {
         mbar_expect_tx(q_full, kQBytes);
         tma_load_2d(sQ, &map_q, q_full, h * HD, rs + q0);
@@ -274,7 +280,11 @@ __global__ void __launch_bounds__(kThreads, 2)
       for (int t = 0; ok && t < n_tiles; ++t) {
         if (t + 1 < n_tiles) {
           // S of tile t has been read by the softmax threads -> QK of tile t+1 may overwrite it
-          if (!mbar_wait(&k_full[(t + 1) & 1], ((t + 1) >> 1) & 1, abort_flag) || !mbar_wait(s_empty, t & 1, abort_flag)) {
+          if (!mbar_wait(&k_full[(t + 1) & 1], ((t + 1) >> 1) & 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(s_empty, t & 1, abort_flag)) {
             ok = false;
             break;
           }
@@ -282,7 +292,11 @@ __global__ void __launch_bounds__(kThreads, 2)
           issue_qk(t + 1);
         }
         // P of tile t is in TMEM (and O has been rescaled where needed); V of tile t has landed
-        if (!mbar_wait(p_full, t & 1, abort_flag) || !mbar_wait(&v_full[t & 1], (t >> 1) & 1, abort_flag)) {
+        if (!mbar_wait(p_full, t & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        if (!mbar_wait(&v_full[t & 1], (t >> 1) & 1, abort_flag)) {
           ok = false;
           break;
         }
@@ -313,9 +327,11 @@ __global__ void __launch_bounds__(kThreads, 2)
     const uint32_t* my_mask = sMask + r * mask_words;  // written and read by this thread only
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+    int site = 0;  // which wait gave up (reported in the status word)
     for (int t = 0; ok && t < n_tiles; ++t) {
       if (!mbar_wait(s_full, t & 1, abort_flag)) {
         ok = false;
+        site = 1;
         break;
       }
       tc_fence_after();
@@ -351,43 +367,52 @@ __global__ void __launch_bounds__(kThreads, 2)
         const int n_in = kv_end - j0;  // 1..63 keys of the tile exist
         vis &= (n_in <= 0) ? 0ull : ((1ull << n_in) - 1ull);
       }
-      // scale, mask, running max
+      // Running max over the RAW scores (the scale is positive), masked keys set to -inf first.
+      // exp2 then takes one FFMA per element: p = 2^(s*scale - m*scale).
       float mx = -INFINITY;
+      if (__all_sync(0xffffffffu, vis == ~0ull)) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        float v = __uint_as_float(sb[i]) * scale_log2;
-        v = ((vis >> i) & 1ull) ? v : -INFINITY;
-        sb[i] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+        for (int i = 0; i < 64; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(sb[i]), __uint_as_float(sb[i + 1])));
+      } else {
+        const uint32_t vlo = (uint32_t)vis, vhi = (uint32_t)(vis >> 32);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (!((vlo >> i) & 1u)) sb[i] = 0xff800000u;
+          if (!((vhi >> i) & 1u)) sb[32 + i] = 0xff800000u;
+        }
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(sb[i]), __uint_as_float(sb[i + 1])));
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
-      const bool moved = (t > 0) && (m_new != m_run);
+      // Lazy running max (in log2 units): it only moves when the tile's max exceeds it by more than
+      // kMaxSlack, so P stays <= 2^kMaxSlack and O is rescaled rarely; l and O use the same max.
+      const float mx2 = mx * scale_log2;
+      const bool moved = mx2 > m_run + kMaxSlack;  // also true for the first visible key (m_run = -inf)
+      const float m_new = moved ? mx2 : m_run;
+      const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_new);
+      const bool rescale = moved && (m_run != -INFINITY);
       m_run = m_new;
-      float rowsum = 0.f;
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+      float rowsum0 = 0.f, rowsum1 = 0.f;
       uint32_t pb[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float p0 = exp2f(__uint_as_float(sb[2 * i]) - m_use);
-        const float p1 = exp2f(__uint_as_float(sb[2 * i + 1]) - m_use);
-        rowsum += p0 + p1;
+        const float p0 = ex2_approx(fmaf(__uint_as_float(sb[2 * i]), scale_log2, neg_m));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(sb[2 * i + 1]), scale_log2, neg_m));
+        rowsum0 += p0;
+        rowsum1 += p1;
         pb[i] = pack_bf16(p0, p1);
       }
-      l_run = l_run * alpha + rowsum;
-      // P buffer t&1 was last read by PV of tile t-2: wait for that product (long done)
-      if (t >= 2 && !mbar_wait(&o_full[t & 1], ((t - 2) >> 1) & 1, abort_flag)) {
-        ok = false;
-        break;
-      }
-      if (__any_sync(0xffffffffu, moved)) {
+      l_run = l_run * (moved ? alpha : 1.0f) + (rowsum0 + rowsum1);
+      // P buffer t&1 was last read by PV of tile t-2, seen complete before this warp's arrival for tile t-1
+      if (__any_sync(0xffffffffu, rescale)) {
         // O must be quiescent while it is rescaled: PV of tile t-1 has to be complete
         if (!mbar_wait(&o_full[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag)) {
           ok = false;
+          site = 3;
           break;
         }
         tc_fence_after();
-        const float a = moved ? alpha : 1.0f;
+        const float a = rescale ? alpha : 1.0f;
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t ob[32];
@@ -399,10 +424,23 @@ __global__ void __launch_bounds__(kThreads, 2)
       }
       tmem_st32(lane_addr + kColP + (t & 1) * 32, pb);
       tc_fence_before();
+      // The arrival for tile t must not be possible before the MMA thread has consumed the barrier's
+      // phase for tile t-1: the thread issues QK of tile t before it looks at that phase, so without
+      // this wait a fast softmax could complete two phases between two of its polls, and a parity
+      // wait cannot tell phase t-1 from phase t+1.  PV of tile t-1 complete implies it was consumed
+      // (and that no warp's arrival for tile t can be counted into the phase of tile t-1).
+      if (t >= 1 && !mbar_wait(&o_full[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag)) {
+        ok = false;
+        site = 4;
+        break;
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag);
+    if (ok && n_tiles > 0) {
+      ok = mbar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag);
+      if (!ok) site = 5;
+    }
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
@@ -424,7 +462,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
       }
     }
-    if (!ok && lane == 0 && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 23);
+    if (!ok && lane == 0 && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 2300 + site);
   }
 
   tc_fence_before();
