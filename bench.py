@@ -182,7 +182,11 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     ms = ev0.elapsed_time(ev1)
     tokens = st.small_host[0].sum().item() - len0
+    kernel_status = int(st.status.item())
     it.close()
+    if kernel_status != 0:
+        # a bounded wait inside a tensor-core kernel gave up: the timing is meaningless
+        raise SystemExit(f"bench: kernel status word {kernel_status} is not zero (a pipeline wait timed out)")
 
     if args.value_only:
         if world > 1:
