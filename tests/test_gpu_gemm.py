@@ -95,6 +95,22 @@ def test_gemm_tc_shapes(M, N, K, live):
     _run(torch.bfloat16, torch.float32, M, N, K, "res", m_live=live, tc=True)
 
 
+@pytest.mark.parametrize(
+    "M,N,K,live,epi,out_dtype",
+    [
+        (1800, 22016, 1024, 761, "swiglu", torch.bfloat16),  # several tiles per CTA pair
+        (1800, 22016, 4096, 1500, "swiglu", torch.bfloat16),  # the stage ring wraps many times
+        (1800, 12288, 512, 900, "none", torch.bfloat16),
+        (1800, 13000, 256, 1800, "bias_silu_res", torch.bfloat16),  # ragged last tile, second half of it empty
+        (400, 40000, 128, None, "res", torch.float32),
+        (1800, 32000, 256, 17, "bias", torch.float32),  # one short chunk
+    ],
+)
+def test_gemm_tc_large_n(M, N, K, live, epi, out_dtype):
+    """Large-N sizes: several tiles per CTA pair, ragged last weight tile, short token chunks."""
+    _run(torch.bfloat16, out_dtype, M, N, K, epi, m_live=live, tc=True)
+
+
 def test_gemm_tc_strided_output():
     """The drafter writes the recurrent state into the right half of a [M, 2H] buffer."""
     from recurrent_drafting import _lib
