@@ -167,6 +167,8 @@ __global__ void __launch_bounds__(kThreads, 2)
                           const int32_t* __restrict__ base_len, int nh, int nkv, int max_len, int mode,
                           const uint32_t* __restrict__ tree_mask, int mask_words, float scale_log2, int32_t* status) {
   const int b = blockIdx.z, h = blockIdx.y;
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();  // row_start, Q and the new K/V rows come from the kernels before this one
   const int rs = row_start[b];
   const int n_new = row_start[b + 1] - rs;
   const int q0 = blockIdx.x * BMQ;
@@ -535,9 +537,13 @@ extern "C" int rd_attention_tc(const void* plan, void* out, const int32_t* row_s
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   dim3 grid((max_new + BMQ - 1) / BMQ, p->nh, p->B);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
-  kern<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(p->map_q, p->map_k, p->map_v, (__nv_bfloat16*)out, row_start,
+  cudaError_t err = rd::launch_chained(kern, grid, dim3(kThreads), kSmemBytes, (cudaStream_t)stream, 1, p->map_q, p->map_k, p->map_v, (__nv_bfloat16*)out, row_start,
                                                              kv_begin, base_len, p->nh, p->nkv, p->max_len, mode, tree_mask,
                                                              mask_words, scale_log2, status);
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   RD_CHECK_LAUNCH();
   return RD_OK;
 }

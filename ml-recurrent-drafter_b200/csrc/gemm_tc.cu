@@ -334,11 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int M = rd::live_rows(m_dev, m_max);
-  const int w_tiles = (N + BM - 1) / BM;
-  const Chunking ch = make_chunking(M, w_tiles, gridDim.x);
-  const int total_tiles = M > 0 ? w_tiles * ch.n_chunks : 0;
-  const int k_blocks = K / BK;
+  rd::pdl_launch_dependents();  // the next kernel may set itself up while this one runs
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -362,6 +358,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched only this CTA's shared memory and TMEM; global memory (the live row
+  // count, the activations, the output) is valid once the kernels before this one have finished
+  rd::pdl_wait();
+  const int M = rd::live_rows(m_dev, m_max);
+  const int w_tiles = (N + BM - 1) / BM;
+  const Chunking ch = make_chunking(M, w_tiles, gridDim.x);
+  const int total_tiles = M > 0 ? w_tiles * ch.n_chunks : 0;
+  const int k_blocks = K / BK;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -581,11 +585,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int M = rd::live_rows(m_dev, m_max);
-  const int w_pairs = (N + 2 * BM - 1) / (2 * BM);
-  const Chunking ch = make_chunking(M, w_pairs, n_pairs);
-  const int total_tiles = M > 0 ? w_pairs * ch.n_chunks : 0;
-  const int k_blocks = K / BK;
+  rd::pdl_launch_dependents();  // the next kernel may set itself up while this one runs
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -610,6 +610,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  rd::pdl_wait();  // global memory is valid once the kernels before this one have finished
+  const int M = rd::live_rows(m_dev, m_max);
+  const int w_pairs = (N + 2 * BM - 1) / (2 * BM);
+  const Chunking ch = make_chunking(M, w_pairs, n_pairs);
+  const int total_tiles = M > 0 ? w_pairs * ch.n_chunks : 0;
+  const int k_blocks = K / BK;
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -779,19 +785,8 @@ template <typename Kern>
 int launch_cluster2(Kern kern, int grid, int smem_bytes, cudaStream_t s, const GemmPlan* p, const EpiArgs& e, const int32_t* m_dev,
                     int32_t* status) {
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem_bytes;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t err = cudaLaunchKernelEx(&cfg, kern, p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K, status);
+  cudaError_t err = rd::launch_chained(kern, dim3(grid), dim3(kThreads), smem_bytes, s, 2, p->map_a, p->map_w, e, p->m_max, m_dev,
+                                       p->N, p->K, status);
   if (err != cudaSuccess) {
     rd_set_last_cuda_error((int)err);
     return RD_ERR_LAUNCH;
@@ -830,11 +825,15 @@ int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t
   if (out_dtype == RD_F32) {
     auto kern = gemm_tc_kernel<EPI, true>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
-    kern<<<grid, kThreads, L::kBytes, s>>>(p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K, status);
+    if (rd::launch_chained(kern, dim3(grid), dim3(kThreads), L::kBytes, s, 1, p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K,
+                           status) != cudaSuccess)
+      return RD_ERR_LAUNCH;
   } else {
     auto kern = gemm_tc_kernel<EPI, false>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
-    kern<<<grid, kThreads, L::kBytes, s>>>(p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K, status);
+    if (rd::launch_chained(kern, dim3(grid), dim3(kThreads), L::kBytes, s, 1, p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K,
+                           status) != cudaSuccess)
+      return RD_ERR_LAUNCH;
   }
   RD_CHECK_LAUNCH();
   return RD_OK;

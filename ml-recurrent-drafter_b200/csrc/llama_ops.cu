@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, c
                                                       int vectorised) {
   constexpr int VEC = 16 / sizeof(T);
   const int t = blockIdx.x;
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   if (t >= rd::live_rows(m_dev, m_max)) return;
   const T* xr = x + (int64_t)t * H;
   T* yr = y + (int64_t)t * H;
@@ -80,6 +82,8 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(
     const int32_t* __restrict__ m_dev, int nh, int nkv, int hd, int max_len) {
   constexpr int VEC = 16 / sizeof(T);
   const int t = blockIdx.x;
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   if (t >= rd::live_rows(m_dev, m_max)) return;
   const int b = tok_row[t], slot = tok_slot[t];
   int pos = tok_pos[t];
@@ -251,9 +255,13 @@ extern "C" int rd_rmsnorm(int dtype, const void* x, const void* weight, void* y,
   cudaStream_t s = (cudaStream_t)stream;
   const int vec = dtype == RD_F32 ? 4 : 8;
   const int vectorised = (H % vec == 0) && (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)y) % 16 == 0);
-  RD_DISPATCH_T(dtype, (rmsnorm_kernel<T><<<m_max, 256, 0, s>>>((const T*)x, (const T*)weight, (T*)y, m_max, m_dev, H, eps,
-                                                                vectorised)));
-  RD_CHECK_LAUNCH();
+  cudaError_t err = cudaSuccess;
+  RD_DISPATCH_T(dtype, (err = rd::launch_chained(rmsnorm_kernel<T>, dim3(m_max), dim3(256), 0, s, 1, (const T*)x, (const T*)weight,
+                                                 (T*)y, m_max, m_dev, H, eps, vectorised)));
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 
@@ -270,10 +278,14 @@ extern "C" int rd_rope_kv_write(int dtype, const void* qkv, void* q_out, void* k
     RD_REQUIRE(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0, RD_ERR_ALIGN);
   }
   cudaStream_t s = (cudaStream_t)stream;
-  RD_DISPATCH_T(dtype, (rope_kv_write_kernel<T><<<m_max, 256, 0, s>>>((const T*)qkv, (T*)q_out, (T*)k_cache, (T*)v_cache,
-                                                                      tok_row, tok_pos, tok_slot, cos_table, sin_table,
-                                                                      n_pos, m_max, m_dev, nh, nkv, hd, max_len)));
-  RD_CHECK_LAUNCH();
+  cudaError_t err = cudaSuccess;
+  RD_DISPATCH_T(dtype, (err = rd::launch_chained(rope_kv_write_kernel<T>, dim3(m_max), dim3(256), 0, s, 1, (const T*)qkv, (T*)q_out,
+                                                 (T*)k_cache, (T*)v_cache, tok_row, tok_pos, tok_slot, cos_table, sin_table,
+                                                 n_pos, m_max, m_dev, nh, nkv, hd, max_len)));
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 

@@ -1,7 +1,16 @@
+#include <stdlib.h>
 // Library-level entry points: error strings, ABI version, last rejected CUDA launch.
 #include "rd_common.cuh"
 
 static thread_local int g_last_cuda_error = 0;
+
+int rd_pdl_enabled() {
+  static int enabled = [] {
+    const char* v = getenv("RD_PDL");
+    return (v && v[0] == '0') ? 0 : 1;
+  }();
+  return enabled;
+}
 
 void rd_set_last_cuda_error(int e) {
   g_last_cuda_error = e;

@@ -26,6 +26,10 @@
   } while (0)
 
 void rd_set_last_cuda_error(int e);
+// 1 unless the environment variable RD_PDL is "0" (read once): launch the kernels of the decode
+// chain with programmatic stream serialisation so that a kernel's launch and prologue overlap the
+// tail of its predecessor.
+int rd_pdl_enabled();
 
 namespace rd {
 
@@ -74,6 +78,41 @@ __device__ __forceinline__ int live_rows(const int* m_dev, int m_max) {
   if (m_dev == nullptr) return m_max;
   int m = *m_dev;
   return m < m_max ? (m < 0 ? 0 : m) : m_max;
+}
+
+// Programmatic dependent launch.  A kernel launched with rd::launch_chained() may begin before the
+// previous kernel of the stream has finished: it must execute pdl_wait() before its first access to
+// global memory (reads of the predecessor's results and writes to anything the predecessor may still
+// read), and it lets its own successor start early with pdl_launch_dependents().  Both are no-ops
+// in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster_x,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (rd_pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 }  // namespace rd
