@@ -190,6 +190,7 @@ class Drafter(torch.nn.Module):
                 "y": [e(M, E), e(M, E), e(M, E)],
                 "logits": e(M, V),
                 "q": [new_sparse(M, dev) for _ in range(Lb - 1)],
+                "q_first": new_sparse(B, dev),  # the first iteration's lists, one per batch row
                 "score": [e(B, W, d=torch.float32), e(B, W, d=torch.float32)],
                 "beams": [torch.zeros(B, W, Lb, dtype=torch.int64, device=dev) for _ in range(2)],
                 "anc": [torch.zeros(B, W, max(Lb - 1, 1), dtype=torch.int32, device=dev) for _ in range(2)],
@@ -240,19 +241,35 @@ class Drafter(torch.nn.Module):
             bin_, bout = ws["beams"][k % 2], ws["beams"][(k + 1) % 2]
             _lib.call("rd_drafter_prepare", code, _lib.ptr(embeddings.weight), _lib.ptr(bin_), _lib.ptr(ws["parent"]),
                       _lib.ptr(ctx), _lib.ptr(a), _lib.ptr(x), B, W, Lb, H, k, st)
+            # In the first iteration every beam of a row holds the same token, state and context
+            # (modeling_drafter.py:170-177), so the W rows of a batch row are identical: compute row 0
+            # of each (a view with row stride W) and copy its results to the others.
+            shared = k == 0 and W > 1
+            rows = slice(None, None, W) if shared else slice(None)
+            a_k, x_k, ys, logits_k = a[rows], x[rows], [y[rows] for y in ws["y"]], ws["logits"][rows]
+            q_k = ws["q_first"] if shared else ws["q"][k]
             # recurrent update, written into the state half of x
-            lin["rnn"](a, x[:, H:], _lib.EPI_BIAS_SILU, ldc=2 * H)
-            cur = x
+            lin["rnn"](a_k, x_k[:, H:], _lib.EPI_BIAS_SILU, ldc=x_k.stride(0))
+            cur = x_k
             yi = 0
             if lin["proj"] is not None:
-                lin["proj"](cur, ws["y"][yi], _lib.EPI_BIAS)
-                cur, yi = ws["y"][yi], yi + 1
+                lin["proj"](cur, ys[yi], _lib.EPI_BIAS)
+                cur, yi = ys[yi], yi + 1
             for res in lin["res"]:
-                nxt = ws["y"][yi % 3]
+                nxt = ys[yi % 3]
                 res(cur, nxt, _lib.EPI_BIAS_SILU_RES, residual=cur)
                 cur, yi = nxt, yi + 1
-            lin["vocab"](cur, ws["logits"])
-            vocab_topk(ws["logits"], ws["q"][k], subtract_max=True)
+            lin["vocab"](cur, logits_k)
+            vocab_topk(logits_k, q_k, subtract_max=True)
+            if shared:
+                q = ws["q"][0]
+                K = q.val.shape[1]
+                q.val.view(B, W, K).copy_(q_k.val.view(B, 1, K).expand(B, W, K))
+                q.idx.view(B, W, K).copy_(q_k.idx.view(B, 1, K).expand(B, W, K))
+                q.cnt.view(B, W).copy_(q_k.cnt.view(B, 1).expand(B, W))
+                q.masked.view(B, W).copy_(q_k.masked.view(B, 1).expand(B, W))
+                xs = x.view(B, W, 2 * H)
+                xs[:, 1:, H:].copy_(xs[:, :1, H:].expand(B, W - 1, H))
             _lib.call("rd_beam_select", B, W, Lb, k, V, _lib.ptr(ws["q"][k].val), _lib.ptr(ws["q"][k].idx),
                       _lib.ptr(ws["q"][k].cnt), _lib.ptr(ws["score"][k % 2]), _lib.ptr(ws["score"][(k + 1) % 2]),
                       _lib.ptr(bin_), _lib.ptr(bout), _lib.ptr(ws["anc"][k % 2]), _lib.ptr(ws["anc"][(k + 1) % 2]),
