@@ -34,7 +34,7 @@ constexpr int kMaxChunk = 256;  // tokens per tile (MMA N), multiple of 16
 constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
-constexpr uint32_t kSpinLimit = 1u << 22;  // polls, each followed by a short sleep
+constexpr uint64_t kWaitLimitNs = 1000000000ull;  // a wait that lasts a second gives up
 
 // Experiment switch: 0 forces the single-CTA kernel (environment RD_GEMM_PAIRS=0, read once).
 static int g_use_pairs = [] {
@@ -70,16 +70,33 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when it gave up or when another role already aborted.
+// One attempt: the hardware may suspend the thread until the phase completes or a time limit of its
+// own expires, so a waiter wakes as soon as the barrier flips instead of at its next poll.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait (kWaitLimitNs).  Returns false when it gave up or when another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) {
-      if (*abort_flag) return false;
-      __nanosleep(64);
-    }
+  if (mbar_test(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kWaitLimitNs) return false;
   }
-  return false;
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
