@@ -526,8 +526,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 // issues the MMAs for both, each CTA's TMEM receives its 128 rows of the accumulator, and each
 // CTA's epilogue warps store their own rows.  Signalling: both CTAs' bulk loads complete on the
 // LEADER's full barrier; the leader frees a stage and publishes an accumulator with one
-// tcgen05.commit per CTA (plain commits to a local and to a peer barrier, no multicast); the
-// peer's epilogue warps release the accumulator with remote arrives on the leader's barrier.
+// tcgen05.commit that arrives on the barrier of both CTAs (the bulk loads themselves are never
+// multicast); the peer's epilogue warps release the accumulator with remote arrives on the
+// leader's barrier.
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -563,9 +564,15 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, 
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
       : "memory");
 }
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
-               : "memory");
+// One commit that arrives on the barrier at the same shared-memory offset in every CTA of `cta_mask`
+// (both CTAs of the pair): half the commit instructions of two plain commits, and commits are not free.
+__device__ __forceinline__ void umma_commit_pair_both(uint64_t* bar) {
+  const uint16_t cta_mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
 }
 __device__ __forceinline__ uint32_t umma_instr_desc_pair(int n) {
   // fp32 accumulator, bf16 A and B, both K-major, M = 256 over the CTA pair, N = n
@@ -573,8 +580,11 @@ __device__ __forceinline__ uint32_t umma_instr_desc_pair(int n) {
 }
 
 struct SmemLayoutPair {
-  static constexpr int kStageW = BM * BK * 2;   // 16 KB: this CTA's 128 weight rows
-  static constexpr int kStageA = 128 * BK * 2;  // 16 KB: this CTA's half of the token tile
+  static constexpr int kSub = 1;                       // k-blocks of 64 per pipeline stage (2 with 3 stages measured the same)
+  static constexpr int kBoxW = BM * BK * 2;            // 16 KB: this CTA's 128 weight rows of one k-block
+  static constexpr int kBoxA = 128 * BK * 2;           // 16 KB: this CTA's half of the token tile of one k-block
+  static constexpr int kStageW = kSub * kBoxW;
+  static constexpr int kStageA = kSub * kBoxA;
   static constexpr int kStages = 6;
   static constexpr int kScratch = 4 * 32 * kScrLd * 4;
   static constexpr int kBytes = kStages * (kStageW + kStageA) + kScratch + 1024 + 256;
@@ -647,15 +657,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int cols = chunk_cols(ch, ci, M);
         const int tok0 = ci * ch.chunk + (int)rank * (cols >> 1);  // this CTA's half of the chunk
         const int w_row0 = w_pair * 2 * BM + (int)rank * BM;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = 0; kb < k_blocks; kb += L::kSub) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
           }
+          const int n_sub = min(L::kSub, k_blocks - kb);
           const uint32_t leader_full = mapa_u32(smem_u32(&full[stage]), 0);
-          if (rank == 0) mbar_expect_tx(&full[stage], 2 * (L::kStageW + L::kStageA));
-          tma_load_2d_pair(sW + stage * L::kStageW, &map_w, leader_full, kb * BK, w_row0);
-          tma_load_2d_pair(sA + stage * L::kStageA, &map_a, leader_full, kb * BK, tok0);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * n_sub * (L::kBoxW + L::kBoxA));
+          for (int sb = 0; sb < n_sub; ++sb) {
+            tma_load_2d_pair(sW + stage * L::kStageW + sb * L::kBoxW, &map_w, leader_full, (kb + sb) * BK, w_row0);
+            tma_load_2d_pair(sA + stage * L::kStageA + sb * L::kBoxA, &map_a, leader_full, (kb + sb) * BK, tok0);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -685,27 +698,27 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kMaxChunk;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = 0; kb < k_blocks; kb += L::kSub) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint64_t dw = umma_smem_desc(smem_u32(sW + stage * L::kStageW));
-          const uint64_t da = umma_smem_desc(smem_u32(sA + stage * L::kStageA));
+          const int n_sub = min(L::kSub, k_blocks - kb);
+          for (int sb = 0; sb < n_sub; ++sb) {
+            const uint64_t dw = umma_smem_desc(smem_u32(sW + stage * L::kStageW + sb * L::kBoxW));
+            const uint64_t da = umma_smem_desc(smem_u32(sA + stage * L::kStageA + sb * L::kBoxA));
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) umma_f16_pair(d_tmem, dw + 2 * k, da + 2 * k, idesc, (kb | k) != 0);
-          // free the stage in both CTAs
-          umma_commit_pair(smem_u32(&empty[stage]));
-          umma_commit_pair(mapa_u32(smem_u32(&empty[stage]), 1));
+            for (int k = 0; k < BK / UMMA_K; ++k) umma_f16_pair(d_tmem, dw + 2 * k, da + 2 * k, idesc, (kb | sb | k) != 0);
+          }
+          umma_commit_pair_both(&empty[stage]);  // frees the stage in both CTAs
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (ok) {
-          umma_commit_pair(smem_u32(&acc_full[acc]));
-          umma_commit_pair(mapa_u32(smem_u32(&acc_full[acc]), 1));
+          umma_commit_pair_both(&acc_full[acc]);
         }
       }
       if (!ok && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 12);
