@@ -181,14 +181,12 @@ __global__ void __launch_bounds__(kThreads, 2)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kQBytes + kStages * kKVStage + kMaskBytes);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;
-  uint64_t* s_empty = bars + 10;
-  uint64_t* p_full = bars + 11;
-  uint64_t* o_full = bars + 12;   // [2]: PV of even / odd tiles
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* v_full = bars + 3;    // [2]
+  uint64_t* s_full = bars + 5;    // [2]: QK^T of even / odd tiles done; also frees that tile's K stage
+  uint64_t* s_empty = bars + 7;
+  uint64_t* p_full = bars + 8;
+  uint64_t* o_full = bars + 9;    // [2]: PV of even / odd tiles done; also frees that tile's V stage
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -202,12 +200,10 @@ __global__ void __launch_bounds__(kThreads, 2)
     mbar_init(q_full, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
       mbar_init(&o_full[s], 1);
     }
-    mbar_init(s_full, 1);
     mbar_init(s_empty, 4);
     mbar_init(p_full, 4);
     *abort_flag = 0;
@@ -233,13 +229,14 @@ __global__ void __launch_bounds__(kThreads, 2)
         tma_load_2d(sQ + BMQ * 128, &map_q, q_full, h * HD + 64, rs + q0);
       }
       uint64_t* full = is_k ? k_full : v_full;
-      uint64_t* empty = is_k ? k_empty : v_empty;
+      // a stage is free when the product that read it is done: QK^T of tile t-2 for K, PV of tile t-2
+      // for V.  Each of these barriers completes once per two tiles, so a parity wait is unambiguous.
+      uint64_t* done = is_k ? s_full : o_full;
       const CUtensorMap* map = is_k ? &map_k : &map_v;
       bool ok = true;
       for (int t = 0; ok && t < n_tiles; ++t) {
         const int s = t & 1;
-        const uint32_t phase = (t >> 1) & 1;
-        if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) {
+        if (t >= kStages && !mbar_wait(&done[s], ((t - 2) >> 1) & 1, abort_flag)) {
           ok = false;
           break;
         }
@@ -269,8 +266,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           const uint64_t db = desc_k_major(smem_u32(sK + (kd >> 2) * kSubTile + (kd & 3) * 32));
           umma_ss(tS, da, db, idesc_qk, kd != 0);
         }
-        umma_commit(s_full);
-        umma_commit(&k_empty[t & 1]);  // the K stage is free once this product is done
+        umma_commit(&s_full[t & 1]);  // S is ready; the K stage is free once this product is done
       };
       if (ok && n_tiles > 0) {
         ok = mbar_wait(&k_full[0], 0, abort_flag);
@@ -311,8 +307,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           const uint64_t dv = desc_mn_major(smem_u32(sV + ks * 2048), kSubTile, 1024);
           umma_ts(tO, tP + (t & 1) * 32 + ks * 8, dv, idesc_pv, (t | ks) != 0);
         }
-        umma_commit(&o_full[t & 1]);
-        umma_commit(&v_empty[t & 1]);
+        umma_commit(&o_full[t & 1]);  // O holds tile t; its P buffer and V stage are free
       }
       if (!ok && atomicCAS((int*)abort_flag, 0, 1) == 0 && status) atomicExch(status, 22);
     }
@@ -331,7 +326,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     bool ok = true;
     int site = 0;  // which wait gave up (reported in the status word)
     for (int t = 0; ok && t < n_tiles; ++t) {
-      if (!mbar_wait(s_full, t & 1, abort_flag)) {
+      if (!mbar_wait(&s_full[t & 1], (t >> 1) & 1, abort_flag)) {
         ok = false;
         site = 1;
         break;
