@@ -74,8 +74,10 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const T* __restrict__ x, c
 
 // One block per token.  A work item is a pair of 16-byte chunks (d .. d+VEC) and (d+hd/2 .. ) of one
 // q or k head - the two halves that the NeoX rotation mixes - or one 16-byte chunk of a v head.
+constexpr int kRopeThreads = 512;
+
 template <typename T>
-__global__ void __launch_bounds__(256) rope_kv_write_kernel(
+__global__ void __launch_bounds__(kRopeThreads) rope_kv_write_kernel(
     const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
     const int32_t* __restrict__ tok_row, const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_slot,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int n_pos, int m_max,
@@ -96,18 +98,39 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(
   const int pairs_per_head = half / VEC;
   const int n_rot = (nh + nkv) * pairs_per_head;
   const int n_v = nkv * (hd / VEC);
-  for (int w = threadIdx.x; w < n_rot + n_v; w += 256) {
+  // 16-byte loads of the fp32 tables need aligned rows
+  const bool vec_tables = (VEC % 4 == 0) && (hd % 4 == 0) && ((((uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0);
+#pragma unroll 2
+  for (int w = threadIdx.x; w < n_rot + n_v; w += kRopeThreads) {
     if (w < n_rot) {
       const int head = w / pairs_per_head, d = (w % pairs_per_head) * VEC;
       T lo[VEC], hi[VEC], olo[VEC], ohi[VEC];
+      float cl[VEC], ch[VEC], sl[VEC], sh[VEC];
       *reinterpret_cast<uint4*>(lo) = *reinterpret_cast<const uint4*>(src + head * hd + d);
       *reinterpret_cast<uint4*>(hi) = *reinterpret_cast<const uint4*>(src + head * hd + d + half);
+      if (vec_tables) {
+#pragma unroll
+        for (int e = 0; e < VEC; e += 4) {
+          *reinterpret_cast<float4*>(cl + e) = *reinterpret_cast<const float4*>(c + d + e);
+          *reinterpret_cast<float4*>(ch + e) = *reinterpret_cast<const float4*>(c + d + half + e);
+          *reinterpret_cast<float4*>(sl + e) = *reinterpret_cast<const float4*>(s + d + e);
+          *reinterpret_cast<float4*>(sh + e) = *reinterpret_cast<const float4*>(s + d + half + e);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          cl[e] = c[d + e];
+          ch[e] = c[d + half + e];
+          sl[e] = s[d + e];
+          sh[e] = s[d + half + e];
+        }
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
         const float x1 = rd::Num<T>::to_f(lo[e]), x2 = rd::Num<T>::to_f(hi[e]);
         // q*cos + rotate_half(q)*sin with two rounded products and one rounded sum
-        olo[e] = rd::Num<T>::from_f(__fadd_rn(__fmul_rn(x1, c[d + e]), __fmul_rn(-x2, s[d + e])));
-        ohi[e] = rd::Num<T>::from_f(__fadd_rn(__fmul_rn(x2, c[d + half + e]), __fmul_rn(x1, s[d + half + e])));
+        olo[e] = rd::Num<T>::from_f(__fadd_rn(__fmul_rn(x1, cl[e]), __fmul_rn(-x2, sl[e])));
+        ohi[e] = rd::Num<T>::from_f(__fadd_rn(__fmul_rn(x2, ch[e]), __fmul_rn(x1, sh[e])));
       }
       T* dst = head < nh ? q_out + (int64_t)t * nh * hd + head * hd
                          : k_cache + (((int64_t)b * nkv + (head - nh)) * max_len + slot) * hd;
@@ -279,7 +302,7 @@ extern "C" int rd_rope_kv_write(int dtype, const void* qkv, void* q_out, void* k
   }
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t err = cudaSuccess;
-  RD_DISPATCH_T(dtype, (err = rd::launch_chained(rope_kv_write_kernel<T>, dim3(m_max), dim3(256), 0, s, 1, (const T*)qkv, (T*)q_out,
+  RD_DISPATCH_T(dtype, (err = rd::launch_chained(rope_kv_write_kernel<T>, dim3(m_max), dim3(kRopeThreads), 0, s, 1, (const T*)qkv, (T*)q_out,
                                                  (T*)k_cache, (T*)v_cache, tok_row, tok_pos, tok_slot, cos_table, sin_table,
                                                  n_pos, m_max, m_dev, nh, nkv, hd, max_len)));
   if (err != cudaSuccess) {
