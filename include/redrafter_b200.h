@@ -211,6 +211,16 @@ RD_API int rd_attention_tc(const void* plan, void* out, const int32_t* row_start
                            const int32_t* base_len, int max_new, int mode, const uint32_t* tree_mask, int mask_words,
                            int32_t* status, void* stream);
 
+/* rd_attention_tc with the key range of every (row, head) cut into n_split shares (1..RD_ATTN_MAX_SPLIT), one CTA
+ * each, merged by a second kernel: for launches with fewer (row, head) pairs than the GPU has SMs and long caches
+ * (batch 1-4).  workspace: rd_attention_split_workspace_bytes(m_max, nh, n_split) bytes of device memory, 16-byte
+ * aligned, holding the shares' unnormalised fp32 outputs, running maxima and sums. */
+#define RD_ATTN_MAX_SPLIT 16
+RD_API int64_t rd_attention_split_workspace_bytes(int m_max, int nh, int n_split);
+RD_API int rd_attention_tc_split(const void* plan, void* out, const int32_t* row_start, const int32_t* kv_begin,
+                          const int32_t* base_len, int max_new, int mode, const uint32_t* tree_mask, int mask_words,
+                          int n_split, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+
 /* argmax_v logits[t, v], first maximal index (torch.argmax, recurrent_drafting.py:52), written
  * to out32 [M] and/or out64 [M] (either may be NULL). */
 RD_API int rd_argmax_rows(const float* logits, int64_t ld, int m_max, const int32_t* m_dev, int V, int32_t* out32,

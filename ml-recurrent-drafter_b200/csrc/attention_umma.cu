@@ -50,7 +50,7 @@ struct AttnPlan {
   CUtensorMap map_q;  // [m_max, nh*128] box 64 x 128
   CUtensorMap map_k;  // [B*nkv*max_len, 128] box 64 x 64
   CUtensorMap map_v;
-  int nh, nkv, max_len, B;
+  int nh, nkv, max_len, B, m_max;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -165,13 +165,15 @@ __global__ void __launch_bounds__(kThreads, 2)
                           const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                           const int32_t* __restrict__ row_start, const int32_t* __restrict__ kv_begin,
                           const int32_t* __restrict__ base_len, int nh, int nkv, int max_len, int mode,
-                          const uint32_t* __restrict__ tree_mask, int mask_words, float scale_log2, int32_t* status) {
+                          const uint32_t* __restrict__ tree_mask, int mask_words, float scale_log2, int32_t* status,
+                          int n_split, float* __restrict__ partial) {
   const int b = blockIdx.z, h = blockIdx.y;
   rd::pdl_launch_dependents();
   rd::pdl_wait();  // row_start, Q and the new K/V rows come from the kernels before this one
   const int rs = row_start[b];
   const int n_new = row_start[b + 1] - rs;
-  const int q0 = blockIdx.x * BMQ;
+  const int q0 = ((int)blockIdx.x / n_split) * BMQ;
+  const int split = (int)blockIdx.x % n_split;  // this CTA's share of the key tiles (1 share = the whole row)
   if (q0 >= n_new) return;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -193,7 +195,20 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int base = base_len[b];
   const int hk = h / (nh / nkv);
   const int kv_end = (mode == RD_ATTN_CAUSAL) ? base + min(n_new, q0 + BMQ) : base + n_new;
-  const int n_tiles = (kv_end + BNK - 1) / BNK;
+  const int all_tiles = (kv_end + BNK - 1) / BNK;
+  const int per_split = (all_tiles + n_split - 1) / n_split;
+  const int t_begin = split * per_split;  // first key tile of this CTA
+  const int n_tiles = max(0, min(per_split, all_tiles - t_begin));
+  if (n_split > 1 && n_tiles == 0) {
+    // nothing to do for this share: leave an empty partial (max = -inf, sum = 0) for the merge
+    const int r = (int)threadIdx.x, qi = q0 + r;
+    if (r < BMQ && qi < n_new) {
+      float* ml = partial + (((int64_t)(rs + qi) * nh + h) * n_split + split) * (HD + 2) + HD;
+      ml[0] = -INFINITY;
+      ml[1] = 0.f;
+    }
+    return;
+  }
   const int kv_row0 = (b * nkv + hk) * max_len + kv_begin[b];  // row of key 0 in the [B*nkv*max_len, 128] view
 
   if (threadIdx.x == 0) {
@@ -242,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
         uint8_t* dst = sKV + s * kKVStage + (is_k ? 0 : 2 * kSubTile);
         mbar_expect_tx(&full[s], 2 * kSubTile);
-        const int row = kv_row0 + t * BNK;
+        const int row = kv_row0 + (t_begin + t) * BNK;
         tma_load_2d(dst, map, &full[s], 0, row);
         tma_load_2d(dst + kSubTile, map, &full[s], 64, row);
       }
@@ -339,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty);
       // visibility of the tile's 64 keys for this row as one 64-bit word
-      const int j0 = t * BNK;
+      const int j0 = (t_begin + t) * BNK;
       uint64_t vis;
       if (j0 + BNK <= base) {
         vis = ~0ull;  // the whole tile lies in the cached prefix
@@ -438,7 +453,25 @@ __global__ void __launch_bounds__(kThreads, 2)
       ok = mbar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag);
       if (!ok) site = 5;
     }
-    if (ok) {
+    if (ok && n_split > 1) {
+      // partial result of this share: unnormalised O (relative to m_run), then m_run and l_run
+      tc_fence_after();
+      float* dstp = partial + (((int64_t)(rs + qi) * nh + h) * n_split + split) * (HD + 2);
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t ob[32];
+        tmem_ld32(lane_addr + kColO + c * 32, ob);
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            *reinterpret_cast<float2*>(dstp + c * 32 + 2 * i) = make_float2(__uint_as_float(ob[2 * i]), __uint_as_float(ob[2 * i + 1]));
+        }
+      }
+      if (live) {
+        dstp[HD] = m_run;
+        dstp[HD + 1] = l_run;
+      }
+    } else if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       uint4* dst = reinterpret_cast<uint4*>(out + ((int64_t)(rs + qi) * nh + h) * HD);
@@ -468,6 +501,24 @@ __global__ void __launch_bounds__(kThreads, 2)
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
+}
+
+// Merge of the shares of a split launch: out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
+__global__ void __launch_bounds__(HD) attention_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                                             const int32_t* __restrict__ row_start, int B, int nh, int n_split) {
+  const int tok = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  if (tok >= row_start[B]) return;
+  const float* p = partial + ((int64_t)tok * nh + h) * n_split * (HD + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < n_split; ++s) m = fmaxf(m, p[s * (HD + 2) + HD]);
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < n_split; ++s) {
+    const float ms = p[s * (HD + 2) + HD];
+    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+    acc += w * p[s * (HD + 2) + d];
+    l += w * p[s * (HD + 2) + HD + 1];
+  }
+  out[((int64_t)tok * nh + h) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -507,6 +558,7 @@ extern "C" void* rd_attention_plan_create(const void* q, int m_max, const void* 
   p->nkv = nkv;
   p->max_len = max_len;
   p->B = B;
+  p->m_max = m_max;
   const int64_t kv_rows = (int64_t)B * nkv * max_len;
   if (!make_map(&p->map_q, q, m_max, (int64_t)nh * HD, (int64_t)nh * HD, BMQ) ||
       !make_map(&p->map_k, k_cache, kv_rows, HD, HD, BNK) || !make_map(&p->map_v, v_cache, kv_rows, HD, HD, BNK)) {
@@ -518,27 +570,55 @@ extern "C" void* rd_attention_plan_create(const void* q, int m_max, const void* 
 
 extern "C" void rd_attention_plan_destroy(void* plan) { delete static_cast<AttnPlan*>(plan); }
 
-extern "C" int rd_attention_tc(const void* plan, void* out, const int32_t* row_start, const int32_t* kv_begin,
+extern "C" int64_t rd_attention_split_workspace_bytes(int m_max, int nh, int n_split);
+
+static int attention_tc_launch(const void* plan, void* out, const int32_t* row_start, const int32_t* kv_begin,
                                const int32_t* base_len, int max_new, int mode, const uint32_t* tree_mask, int mask_words,
-                               int32_t* status, void* stream) {
+                               int n_split, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
   RD_REQUIRE(plan && out && row_start && kv_begin && base_len, RD_ERR_ARG);
   RD_REQUIRE(mode == RD_ATTN_CAUSAL || (mode == RD_ATTN_TREE && tree_mask && mask_words >= 1 && mask_words <= kMaxMaskWords),
              RD_ERR_ARG);
-  RD_REQUIRE(max_new >= 1, RD_ERR_SIZE);
+  RD_REQUIRE(max_new >= 1 && n_split >= 1 && n_split <= RD_ATTN_MAX_SPLIT, RD_ERR_SIZE);
   RD_REQUIRE(((uintptr_t)out & 15) == 0, RD_ERR_ALIGN);
   const AttnPlan* p = static_cast<const AttnPlan*>(plan);
   RD_REQUIRE(p->B <= 65535 && p->nh <= 65535, RD_ERR_SIZE);
+  if (n_split > 1) {
+    RD_REQUIRE(workspace && ((uintptr_t)workspace & 15) == 0, RD_ERR_ARG);
+    RD_REQUIRE(workspace_bytes >= rd_attention_split_workspace_bytes(p->m_max, p->nh, n_split), RD_ERR_CAPACITY);
+  }
   auto kern = attention_umma_kernel;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  dim3 grid((max_new + BMQ - 1) / BMQ, p->nh, p->B);
+  dim3 grid(((max_new + BMQ - 1) / BMQ) * n_split, p->nh, p->B);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
-  cudaError_t err = rd::launch_chained(kern, grid, dim3(kThreads), kSmemBytes, (cudaStream_t)stream, 1, p->map_q, p->map_k, p->map_v, (__nv_bfloat16*)out, row_start,
-                                                             kv_begin, base_len, p->nh, p->nkv, p->max_len, mode, tree_mask,
-                                                             mask_words, scale_log2, status);
+  cudaError_t err = rd::launch_chained(kern, grid, dim3(kThreads), kSmemBytes, (cudaStream_t)stream, 1, p->map_q, p->map_k, p->map_v,
+                                       (__nv_bfloat16*)out, row_start, kv_begin, base_len, p->nh, p->nkv, p->max_len, mode,
+                                       tree_mask, mask_words, scale_log2, status, n_split, (float*)workspace);
   if (err != cudaSuccess) {
     rd_set_last_cuda_error((int)err);
     return RD_ERR_LAUNCH;
   }
+  if (n_split > 1) {
+    attention_merge_kernel<<<dim3(p->m_max, p->nh), HD, 0, (cudaStream_t)stream>>>((const float*)workspace, (__nv_bfloat16*)out,
+                                                                                 row_start, p->B, p->nh, n_split);
+  }
   RD_CHECK_LAUNCH();
   return RD_OK;
+}
+
+extern "C" int64_t rd_attention_split_workspace_bytes(int m_max, int nh, int n_split) {
+  return (int64_t)m_max * nh * n_split * (HD + 2) * (int64_t)sizeof(float);
+}
+
+extern "C" int rd_attention_tc(const void* plan, void* out, const int32_t* row_start, const int32_t* kv_begin,
+                               const int32_t* base_len, int max_new, int mode, const uint32_t* tree_mask, int mask_words,
+                               int32_t* status, void* stream) {
+  return attention_tc_launch(plan, out, row_start, kv_begin, base_len, max_new, mode, tree_mask, mask_words, 1, nullptr, 0,
+                             status, stream);
+}
+
+extern "C" int rd_attention_tc_split(const void* plan, void* out, const int32_t* row_start, const int32_t* kv_begin,
+                                     const int32_t* base_len, int max_new, int mode, const uint32_t* tree_mask, int mask_words,
+                                     int n_split, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  return attention_tc_launch(plan, out, row_start, kv_begin, base_len, max_new, mode, tree_mask, mask_words, n_split, workspace,
+                             workspace_bytes, status, stream);
 }

@@ -113,9 +113,18 @@ def run_cell(B: int, W: int, Lb: int, S: int, timer: Timer, hbm_peak: float) -> 
     if not plan:
         raise _lib.RedrafterError("rd_attention_plan_create failed")
 
+    shares = rd.attention.key_range_shares(B, NH, W * Lb, S + W * Lb)
+    ws_bytes = lib.rd_attention_split_workspace_bytes(cap, NH, shares) if shares > 1 else 0
+    split_ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+
     def attn():
-        _lib.call("rd_attention_tc", plan, _lib.ptr(out), _lib.ptr(fp.row_start), _lib.ptr(kv_begin), _lib.ptr(fp.base_len),
-                  W * Lb, _lib.ATTN_TREE, _lib.ptr(fp.tree_mask), fp.mask_words, _lib.ptr(status), _lib.stream())
+        if shares > 1:
+            _lib.call("rd_attention_tc_split", plan, _lib.ptr(out), _lib.ptr(fp.row_start), _lib.ptr(kv_begin), _lib.ptr(fp.base_len),
+                      W * Lb, _lib.ATTN_TREE, _lib.ptr(fp.tree_mask), fp.mask_words, shares, _lib.ptr(split_ws), ws_bytes,
+                      _lib.ptr(status), _lib.stream())
+        else:
+            _lib.call("rd_attention_tc", plan, _lib.ptr(out), _lib.ptr(fp.row_start), _lib.ptr(kv_begin), _lib.ptr(fp.base_len),
+                      W * Lb, _lib.ATTN_TREE, _lib.ptr(fp.tree_mask), fp.mask_words, _lib.ptr(status), _lib.stream())
 
     t_attn = timer(attn)
     lib.rd_attention_plan_destroy(plan)
@@ -123,7 +132,7 @@ def run_cell(B: int, W: int, Lb: int, S: int, timer: Timer, hbm_peak: float) -> 
         raise _lib.RedrafterError(f"attention kernel status {int(status.item())}")
     attn_bytes = (2 * NKV * int((S + n_sel).sum()) * HD + 2 * M * NH * HD) * 2
     attn_flops = 4 * NH * HD * int((n_sel * (S + n_sel)).sum())
-    del q, out
+    del q, out, split_ws
 
     # ---- acceptance: row argmax over fp32 logits, then choice + commit
     logits = torch.randn(M, V, device=dev)
@@ -170,7 +179,7 @@ def run_cell(B: int, W: int, Lb: int, S: int, timer: Timer, hbm_peak: float) -> 
         "B": B, "W": W, "Lb": Lb, "S": S, "tokens": M, "shared_prefix_fraction": round(shared, 3),
         "mean_accepted": round(float(acc.mean()), 2), "commit_layers": NL,
         "pack_us": round(t_pack, 1), "pack_gbs": round(gbs(pack_bytes, t_pack), 1),
-        "attn_us": round(t_attn, 1), "attn_gbs": round(gbs(attn_bytes, t_attn), 1),
+        "attn_shares": shares, "attn_us": round(t_attn, 1), "attn_gbs": round(gbs(attn_bytes, t_attn), 1),
         "attn_frac_hbm": round(gbs(attn_bytes, t_attn) / hbm_peak, 3), "attn_tflops": round(attn_flops / (t_attn * 1e-6) / 1e12, 1),
         "argmax_us": round(t_argmax, 1), "argmax_gbs": round(gbs(argmax_bytes, t_argmax), 1),
         "argmax_frac_hbm": round(gbs(argmax_bytes, t_argmax) / hbm_peak, 3),
@@ -194,7 +203,7 @@ def main() -> None:
     if args.quick:
         Bs, Ws, Ls, Ss = [1, 64], [8, 64], [3, 7], [512, 4096]
     timer = Timer(args.reps)
-    cols = ["B", "W", "Lb", "S", "tokens", "shared_prefix_fraction", "mean_accepted", "pack_us", "attn_us", "attn_gbs",
+    cols = ["B", "W", "Lb", "S", "tokens", "shared_prefix_fraction", "mean_accepted", "pack_us", "attn_shares", "attn_us", "attn_gbs",
             "attn_frac_hbm", "attn_tflops", "argmax_us", "argmax_gbs", "argmax_frac_hbm", "commit_layers", "commit_us", "commit_gbs"]
     lines = [f"HBM peak {hbm_peak:.1f} GB/s ({src})", "", "| " + " | ".join(cols) + " |", "|" + "---|" * len(cols)]
     for B in Bs:

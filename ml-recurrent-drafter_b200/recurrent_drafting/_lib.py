@@ -45,6 +45,8 @@ SIGNATURES = {
     "rd_attention_plan_create": (_P, [_P, _I, _P, _P, _I, _I, _I, _I, _I]),
     "rd_attention_plan_destroy": (None, [_P]),
     "rd_attention_tc": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _I, _P, _P]),
+    "rd_attention_split_workspace_bytes": (_L, [_I, _I, _I]),
+    "rd_attention_tc_split": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P, _L, _P, _P]),
     "rd_argmax_rows": (_I, [_P, _L, _I, _P, _I, _P, _P, _P]),
     "rd_accept_commit_greedy": (_I, [_I, _P, _I, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "rd_commit_reference_slots": (_I, [_I, _I, _I, _P, _P, _P, _I, _I, _P, _P]),

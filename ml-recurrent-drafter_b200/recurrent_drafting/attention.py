@@ -31,3 +31,20 @@ def bias(causal_mask: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """0 where visible, the dtype's most negative finite value elsewhere (attention.py:75-88)."""
     out = torch.zeros(causal_mask.shape, dtype=dtype, device=causal_mask.device)
     return out.masked_fill_(causal_mask.logical_not(), torch.finfo(dtype).min)
+
+
+ATTN_MAX_SPLIT = 16
+
+
+def key_range_shares(batch: int, n_heads: int, max_new: int, max_kv: int, n_sm: int = 148) -> int:
+    """How many CTAs should share the key range of one (row, head) in the tcgen05 attention
+    (rd_attention_tc_split).  One, unless the launch has fewer (row, head, query tile) chains than
+    the GPU can hold at two CTAs per SM: then enough shares to fill it, each with at least four key
+    tiles of 64."""
+    chains = batch * n_heads * ((max_new + 127) // 128)
+    slots = 2 * n_sm
+    if chains >= slots // 2:
+        return 1
+    by_fill = slots // chains
+    by_length = max(1, ((max_kv + 63) // 64) // 4)
+    return max(1, min(ATTN_MAX_SPLIT, by_fill, by_length))

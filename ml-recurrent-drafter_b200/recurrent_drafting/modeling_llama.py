@@ -19,7 +19,7 @@ import torch
 from torch import nn
 from transformers.modeling_outputs import CausalLMOutput
 
-from . import _lib, kv_cache
+from . import _lib, attention, kv_cache
 
 
 class _Linear:
@@ -136,6 +136,7 @@ class LlamaForCausalLM(nn.Module):
         self._linears = None
         self._rope = None
         self._attn_plans: Dict[Tuple, int] = {}
+        self._attn_split_ws: Optional[torch.Tensor] = None
         self.gemm_status: Optional[torch.Tensor] = None
 
     # ----------------------------------------------------------------- reference-compatible surface
@@ -256,8 +257,18 @@ class LlamaForCausalLM(nn.Module):
                 if len(self._attn_plans) > 4096:
                     self._drop_attn_plans()
                 self._attn_plans[key] = plan
-            _lib.call("rd_attention_tc", plan, _lib.ptr(attn), _lib.ptr(row_start), _lib.ptr(kv_begin), _lib.ptr(base_len), max_new,
-                      mode, _lib.ptr(tree_mask), mask_words, _lib.ptr(self.gemm_status), st)
+            shares = attention.key_range_shares(batch, nh, max_new, max_kv)
+            if shares > 1:
+                # few (row, head) chains and a long cache: several CTAs per chain, merged by a second kernel
+                need = _lib.load().rd_attention_split_workspace_bytes(m_max, nh, shares)
+                if self._attn_split_ws is None or self._attn_split_ws.numel() < need:
+                    self._attn_split_ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+                _lib.call("rd_attention_tc_split", plan, _lib.ptr(attn), _lib.ptr(row_start), _lib.ptr(kv_begin), _lib.ptr(base_len),
+                          max_new, mode, _lib.ptr(tree_mask), mask_words, shares, _lib.ptr(self._attn_split_ws),
+                          self._attn_split_ws.numel(), _lib.ptr(self.gemm_status), st)
+            else:
+                _lib.call("rd_attention_tc", plan, _lib.ptr(attn), _lib.ptr(row_start), _lib.ptr(kv_begin), _lib.ptr(base_len),
+                          max_new, mode, _lib.ptr(tree_mask), mask_words, _lib.ptr(self.gemm_status), st)
             return
         _lib.call("rd_attention", code, _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(attn), _lib.ptr(row_start),
                   _lib.ptr(kv_begin), _lib.ptr(base_len), batch, nh, nkv, hd, max_len, max_new, max_kv, mode,

@@ -139,3 +139,46 @@ def test_tree_attention_is_repeatable_over_many_launches():
     lib.rd_attention_plan_destroy(plan)
     assert int(status.item()) == 0
     assert int(mismatches.item()) == 0
+
+
+@pytest.mark.parametrize("mode", ["tree", "causal"])
+@pytest.mark.parametrize("B,W,L,S,shares", [(1, 45, 5, 2048, 8), (2, 8, 3, 700, 3), (1, 64, 7, 300, 16), (3, 45, 5, 100, 4)])
+def test_attention_with_shared_key_range_matches_the_single_cta_form(B, W, L, S, shares, mode):
+    """rd_attention_tc_split: several CTAs share the keys of a (row, head) and a merge kernel combines
+    them; also shares that get no key tile at all (more shares than tiles).  Compared with the
+    unsplit kernel (tight) - which the tests above compare with the fp32 reference."""
+    import recurrent_drafting as rd
+    from recurrent_drafting import _lib
+
+    dev = "cuda"
+    beams = torch.from_numpy(mb.zipf_beams(B, W, L, 32000, 5 + B, branch=9)).to(dev)
+    max_len = S + W * L
+    cap = B * W * L
+    g = torch.Generator(device=dev).manual_seed(31)
+    q = torch.randn(cap, NH * HD, device=dev, generator=g).bfloat16()
+    k = torch.randn(B, NKV, max_len, HD, device=dev, generator=g).bfloat16()
+    v = torch.randn(B, NKV, max_len, HD, device=dev, generator=g).bfloat16()
+    kv_begin = torch.zeros(B, dtype=torch.int32, device=dev)
+    kv_len = torch.full((B,), S, dtype=torch.int32, device=dev)
+    fp = rd.tree_attention.pack_flat(beams, kv_begin, kv_len)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    plan = lib.rd_attention_plan_create(_lib.ptr(q), cap, _lib.ptr(k), _lib.ptr(v), B, NH, NKV, HD, max_len)
+    assert plan
+    code = _lib.ATTN_TREE if mode == "tree" else _lib.ATTN_CAUSAL
+    one = torch.zeros(cap, NH * HD, dtype=torch.bfloat16, device=dev)
+    many = torch.zeros(cap, NH * HD, dtype=torch.bfloat16, device=dev)
+    _lib.call("rd_attention_tc", plan, _lib.ptr(one), _lib.ptr(fp.row_start), _lib.ptr(kv_begin), _lib.ptr(fp.base_len), W * L, code,
+              _lib.ptr(fp.tree_mask), fp.mask_words, _lib.ptr(status), _lib.stream())
+    need = lib.rd_attention_split_workspace_bytes(cap, NH, shares)
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    _lib.call("rd_attention_tc_split", plan, _lib.ptr(many), _lib.ptr(fp.row_start), _lib.ptr(kv_begin), _lib.ptr(fp.base_len), W * L,
+              code, _lib.ptr(fp.tree_mask), fp.mask_words, shares, _lib.ptr(ws), need, _lib.ptr(status), _lib.stream())
+    with pytest.raises(_lib.RedrafterError):  # a workspace that is too small is refused on the host
+        _lib.call("rd_attention_tc_split", plan, _lib.ptr(many), _lib.ptr(fp.row_start), _lib.ptr(kv_begin), _lib.ptr(fp.base_len),
+                  W * L, code, _lib.ptr(fp.tree_mask), fp.mask_words, shares, _lib.ptr(ws), need - 1, _lib.ptr(status), _lib.stream())
+    torch.cuda.synchronize()
+    lib.rd_attention_plan_destroy(plan)
+    assert int(status.item()) == 0
+    M = int(fp.row_start[-1].item())
+    torch.testing.assert_close(many[:M].float(), one[:M].float(), rtol=2e-2, atol=1e-2)
