@@ -141,27 +141,30 @@ __device__ void pack_row_emit(const PackArgs& a, int b, int lane, int rs) {
   }
 }
 
-__global__ void __launch_bounds__(1024) tree_pack_kernel(PackArgs a) {
-  extern __shared__ int32_t smem[];
-  int32_t* seg = smem;                 // [32 warps][64]
-  int32_t* nsel = smem + 32 * 64;      // [B]
-  int32_t* rstart = nsel + a.B;        // [B+1]
+constexpr int kRowsPerCta = 4;  // one warp per batch row
+
+// Phase A: prefix ids, unpacker and n_selected of every row (rows are independent).
+__global__ void __launch_bounds__(kRowsPerCta * 32) tree_pack_ids_kernel(PackArgs a) {
+  __shared__ int32_t seg[kRowsPerCta][64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int b = warp; b < a.B; b += 32) pack_row_ids(a, b, lane, seg + warp * 64);
-  __syncthreads();
-  // exclusive scan of n_selected over the batch (B is small; one thread)
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int b = 0; b < a.B; ++b) {
-      rstart[b] = acc;
-      a.row_start[b] = acc;
-      acc += a.n_selected[b];
-    }
-    rstart[a.B] = acc;
-    a.row_start[a.B] = acc;
+  const int b = blockIdx.x * kRowsPerCta + warp;
+  if (b < a.B) pack_row_ids(a, b, lane, seg[warp]);
+}
+
+// Phase B: each warp sums the counts of the rows before its own (the batch is small), publishes
+// row_start and writes its row's slice of the flat arrays and the bitmask.
+__global__ void __launch_bounds__(kRowsPerCta * 32) tree_pack_emit_kernel(PackArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x * kRowsPerCta + warp;
+  if (b >= a.B) return;
+  int before = 0;
+  for (int r = lane; r < b; r += 32) before += a.n_selected[r];
+  before = rd::warp_sum_i(before);
+  if (lane == 0) {
+    a.row_start[b] = before;
+    if (b == a.B - 1) a.row_start[a.B] = before + a.n_selected[b];
   }
-  __syncthreads();
-  for (int b = warp; b < a.B; b += 32) pack_row_emit(a, b, lane, rstart[b]);
+  pack_row_emit(a, b, lane, before);
 }
 
 struct RefArgs {
@@ -227,8 +230,9 @@ extern "C" int rd_tree_pack(const int64_t* beams, int B, int W, int Lb, const in
   RD_REQUIRE(mask_words * 32 >= W * Lb, RD_ERR_SIZE);
   PackArgs a{beams,      B,          W,       Lb,      kv_begin, kv_len,    prefix_tree, unpacker,  n_selected,
              row_start,  flat_tokens, flat_index, tok_row, tok_pos,  tok_slot,  tree_mask,   mask_words, base_len};
-  size_t smem = (size_t)(32 * 64 + 2 * B + 1) * sizeof(int32_t);
-  tree_pack_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>(a);
+  const int grid = (B + kRowsPerCta - 1) / kRowsPerCta;
+  tree_pack_ids_kernel<<<grid, kRowsPerCta * 32, 0, (cudaStream_t)stream>>>(a);
+  tree_pack_emit_kernel<<<grid, kRowsPerCta * 32, 0, (cudaStream_t)stream>>>(a);
   RD_CHECK_LAUNCH();
   return RD_OK;
 }
