@@ -359,6 +359,18 @@ __global__ void __launch_bounds__(kSelThreads) beam_select_kernel(
       // entries of list o that precede (s, w): score > s, or score == s when o < w
       const float* lo_list = cs + o * W;
       int lo = 0, hi = len[o];
+      // the lists are sorted: most of them contribute nothing (head does not precede) or everything
+      if (hi == 0) continue;
+      {
+        const float head = lo_list[0], tail = lo_list[hi - 1];
+        if (!((o < w) ? (head >= s) : (head > s))) continue;
+        if ((o < w) ? (tail >= s) : (tail > s)) {
+          rank += hi;
+          continue;
+        }
+        lo = 1;
+        hi = hi - 1;
+      }
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
         const float v = lo_list[mid];
