@@ -198,22 +198,42 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
   // 1. thread maxima -> lower bound T0 of the K-th largest value, and the row maximum
   float lm = -INFINITY;
   row.for_each(tid, [&](float f, int) { lm = fmaxf(lm, f); });
-  sh.lmax[tid] = lm;
   if (tid == 0) {
     sh.ccount = 0;
     sh.gt = 0;
     sh.ties = 0;
     sh.t0 = -INFINITY;
   }
-  __syncthreads();
+  // Each warp publishes its four largest thread maxima: kTopkThreads / 8 = 64 distinct elements of
+  // the row, so the K-th largest of them (K <= 64) cannot exceed the K-th largest of the row.
   {
-    int rank = 0;
-    for (int o = 0; o < kTopkThreads; ++o) {
-      const float v = sh.lmax[o];
-      rank += (v > lm) || (v == lm && o < tid);
+    float v = lm;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float m = rd::warp_max(v);
+      const uint32_t eq = __ballot_sync(0xffffffffu, v == m);
+      if (lane == 0) sh.lmax[warp * 4 + r] = m;
+      if (lane == __ffs(eq) - 1) v = -INFINITY;  // retire one holder of the maximum
     }
-    if (rank == 0) sh.mx = lm;
-    if (rank == K - 1 && lm > -INFINITY) sh.t0 = lm;  // stays -inf when fewer than K threads hold elements
+  }
+  __syncthreads();
+  if (warp == 0) {
+    constexpr int kVals = kTopkThreads / 8;  // 64
+    float best = -INFINITY;
+#pragma unroll
+    for (int h = 0; h < kVals / 32; ++h) {
+      const int me = h * 32 + lane;
+      const float mv = sh.lmax[me];
+      best = fmaxf(best, mv);
+      int rank = 0;
+      for (int o = 0; o < kVals; ++o) {
+        const float ov = sh.lmax[o];
+        rank += (ov > mv) || (ov == mv && o < me);
+      }
+      if (rank == K - 1 && mv > -INFINITY) sh.t0 = mv;  // stays -inf when fewer than K values exist
+    }
+    best = rd::warp_max(best);
+    if (lane == 0) sh.mx = best;
   }
   __syncthreads();
   const float t0 = sh.t0, mx = sh.mx;
