@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------
-// rd_beam_select: one block per batch row.
+// rd_beam_select: kSelSplit blocks per batch row (each holds all lists, ranks a share of the candidates).
 //
 // Every row's kept list is sorted by (log-prob descending, id ascending), so adding the row's beam
 // score keeps it non-increasing.  The candidates' total order is (score descending, beam index
@@ -345,7 +345,8 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
 // order, for equal scores it is the flat-index order w*V+token whenever the tie is exact in the
 // log-probs as well.  A candidate's rank is its own position plus, for every other beam, the number
 // of entries that precede it, found by binary search; ranks below W are the new beams.
-constexpr int kSelThreads = 1024;
+constexpr int kSelThreads = 256;
+constexpr int kSelSplit = 8;  // CTAs per batch row: each ranks its share of the candidates against all lists
 
 __global__ void __launch_bounds__(kSelThreads) beam_select_kernel(
     int W, int Lb, int k, int V, const float* __restrict__ kept_val, const int32_t* __restrict__ kept_idx,
@@ -369,7 +370,7 @@ __global__ void __launch_bounds__(kSelThreads) beam_select_kernel(
     cs[c] = (i < len[w]) ? kept_val[(int64_t)r * kKept + i] + base : -INFINITY;
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < ncand; c += kSelThreads) {
+  for (int c = blockIdx.y * kSelThreads + threadIdx.x; c < ncand; c += kSelThreads * gridDim.y) {
     const int w = c / W, i = c % W;
     if (i >= len[w]) continue;
     const float s = cs[c];
@@ -537,7 +538,7 @@ extern "C" int rd_beam_select(int B, int W, int Lb, int k, int V, const float* k
              RD_ERR_SIZE);
   RD_REQUIRE((int64_t)W * V < (int64_t)INT32_MAX, RD_ERR_SIZE);
   const size_t smem = (size_t)W * W * sizeof(float) + (size_t)W * sizeof(int);
-  beam_select_kernel<<<B, kSelThreads, smem, (cudaStream_t)stream>>>(W, Lb, k, V, kept_val, kept_idx, kept_cnt, score_in,
+  beam_select_kernel<<<dim3(B, kSelSplit), kSelThreads, smem, (cudaStream_t)stream>>>(W, Lb, k, V, kept_val, kept_idx, kept_cnt, score_in,
                                                                     score_out, beams_in, beams_out, anc_in, anc_out,
                                                                     parent_out);
   RD_CHECK_LAUNCH();
