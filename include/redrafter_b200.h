@@ -164,6 +164,17 @@ RD_API void rd_gemm_plan_destroy(void* plan);
 RD_API int rd_gemm_bf16_tc(const void* plan, int out_dtype, void* C, int64_t ldc, const void* bias, const void* R,
                     int64_t ldr, const int32_t* m_dev, int epilogue, int32_t* status, void* stream);
 
+/* The QKV projection (modeling_llama.py:141-143) with apply_rotary_pos_emb (:104-110) and the cache
+ * append (:157-159) done in its epilogue: `plan` holds (normed activations, packed [q;k;v] weight
+ * of (nh + 2 nkv) * 128 rows); rotated Q rows go to q_out [m, nh*128], rotated K and plain V rows
+ * to the caches [B, nkv, max_len, 128] at tok_slot of row tok_row, positions from tok_pos into the
+ * fp32 cos/sin tables [n_pos, 128].  head_dim 128, bf16.  Same result, bit for bit, as
+ * rd_gemm_bf16_tc followed by rd_rope_kv_write. */
+RD_API int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, void* q_out, void* k_cache, void* v_cache,
+                             const int32_t* tok_row, const int32_t* tok_pos, const int32_t* tok_slot,
+                             const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv, int hd,
+                             int max_len, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Llama verify forward pieces (recurrent_drafting/modeling_llama.py). */
 

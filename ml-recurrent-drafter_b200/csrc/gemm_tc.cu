@@ -189,7 +189,20 @@ struct EpiArgs {
   const __nv_bfloat16* bias;
   const void* R;
   int64_t ldr;
+  // kEpiQkvRope only: the QKV projection whose epilogue applies the rotary embedding and writes
+  // Q rows [tok, head*128 + d] and the K/V cache rows of the token's slot (head_dim 128, bf16)
+  __nv_bfloat16* q_out;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  const int32_t* tok_row;
+  const int32_t* tok_pos;
+  const int32_t* tok_slot;
+  const float* cos_t;
+  const float* sin_t;
+  int n_pos, nh, nkv, max_len;
 };
+
+constexpr int kEpiQkvRope = 6;  // internal epilogue code (not one of RD_EPI_*): reached through rd_gemm_bf16_tc_qkv_rope
 
 constexpr int kScrLd = 36;  // floats per scratch row: 16-byte aligned rows, conflict-free float4 reads
 
@@ -321,6 +334,74 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
     }
   }
   (void)n_out_total;
+}
+
+// Epilogue block of the QKV projection with fused rotary embedding (head_dim 128 = one CTA's 128
+// weight rows = one head).  v: this lane's feature d = 32*quarter + lane for the block's 32 tokens.
+// The rotation pairs feature d with d +- 64, which lives in the warp two quarters away, so the four
+// epilogue warps exchange their transposed blocks through the scratch and meet at a named barrier.
+// Values are rounded to bf16 first, as a separate projection would have stored them, so the result
+// equals projection -> rope bit for bit.
+__device__ __forceinline__ void epilogue_rope_block(const float* v, const EpiArgs& e, float* scr_all, int quarter, int lane,
+                                                    int head, int tok0, int tok_limit) {
+  float* scr = scr_all + quarter * 32 * kScrLd;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = __bfloat162float(__float2bfloat16_rn(v[i]));
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  const bool is_v = head >= e.nh + e.nkv;
+  float o[32], p[32];
+  const float* own = scr + lane * kScrLd;
+  const float* oth = scr_all + (quarter ^ 2) * 32 * kScrLd + lane * kScrLd;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float4 f = *reinterpret_cast<const float4*>(own + 4 * j);
+    o[4 * j] = f.x;
+    o[4 * j + 1] = f.y;
+    o[4 * j + 2] = f.z;
+    o[4 * j + 3] = f.w;
+    const float4 g = is_v ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(oth + 4 * j);
+    p[4 * j] = g.x;
+    p[4 * j + 1] = g.y;
+    p[4 * j + 2] = g.z;
+    p[4 * j + 3] = g.w;
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");  // all four warps have read before the scratch is reused
+  const int tok = tok0 + lane;
+  if (tok >= tok_limit) return;
+  const int d0 = quarter * 32;
+  if (!is_v) {
+    int pos = e.tok_pos[tok];
+    pos = pos < 0 ? 0 : (pos >= e.n_pos ? e.n_pos - 1 : pos);
+    const float4* c4 = reinterpret_cast<const float4*>(e.cos_t + (int64_t)pos * 128 + d0);
+    const float4* s4 = reinterpret_cast<const float4*>(e.sin_t + (int64_t)pos * 128 + d0);
+    const float sign = quarter < 2 ? -1.0f : 1.0f;  // rotate_half: (-x2, x1)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 c = c4[j], sn = s4[j];
+      // two rounded products and one rounded sum, as the separate rope kernel computes them
+      o[4 * j] = __fadd_rn(__fmul_rn(o[4 * j], c.x), __fmul_rn(sign * p[4 * j], sn.x));
+      o[4 * j + 1] = __fadd_rn(__fmul_rn(o[4 * j + 1], c.y), __fmul_rn(sign * p[4 * j + 1], sn.y));
+      o[4 * j + 2] = __fadd_rn(__fmul_rn(o[4 * j + 2], c.z), __fmul_rn(sign * p[4 * j + 2], sn.z));
+      o[4 * j + 3] = __fadd_rn(__fmul_rn(o[4 * j + 3], c.w), __fmul_rn(sign * p[4 * j + 3], sn.w));
+    }
+  }
+  __nv_bfloat16* dst;
+  if (head < e.nh) {
+    dst = e.q_out + ((int64_t)tok * e.nh + head) * 128 + d0;
+  } else {
+    const int b = e.tok_row[tok], slot = e.tok_slot[tok];
+    const int kvh = is_v ? head - e.nh - e.nkv : head - e.nh;
+    dst = (is_v ? e.v_cache : e.k_cache) + (((int64_t)b * e.nkv + kvh) * e.max_len + slot) * 128 + d0;
+  }
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 pk;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(o[8 * j + 2 * t], o[8 * j + 2 * t + 1]);
+    d4[j] = pk;
+  }
 }
 
 struct SmemLayout {
@@ -500,8 +581,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        epilogue_math<EPI>(v, epi, n_warp0 + lane, N);
-        epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
+        if (EPI == kEpiQkvRope) {
+          epilogue_rope_block(v, epi, scratch, quarter, lane, (n_warp0 - quarter * 32) / 128, tok_base + c, tok_limit);
+        } else {
+          epilogue_math<EPI>(v, epi, n_warp0 + lane, N);
+          epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -762,8 +847,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        epilogue_math<EPI>(v, epi, n_warp0 + lane, N);
-        epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
+        if (EPI == kEpiQkvRope) {
+          epilogue_rope_block(v, epi, scratch, quarter, lane, (n_warp0 - quarter * 32) / 128, tok_base + c, tok_limit);
+        } else {
+          epilogue_math<EPI>(v, epi, n_warp0 + lane, N);
+          epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -878,6 +967,7 @@ int launch_epi(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t
     case RD_EPI_BIAS_SILU_RES: return launch_out<RD_EPI_BIAS_SILU_RES>(p, out_dtype, e, m_dev, status, s);
     case RD_EPI_RES: return launch_out<RD_EPI_RES>(p, out_dtype, e, m_dev, status, s);
     case RD_EPI_SWIGLU: return launch_out<RD_EPI_SWIGLU>(p, out_dtype, e, m_dev, status, s);
+    case kEpiQkvRope: return launch_out<kEpiQkvRope>(p, out_dtype, e, m_dev, status, s);
     default: return RD_ERR_ARG;
   }
 }
@@ -910,7 +1000,40 @@ extern "C" int rd_gemm_bf16_tc(const void* plan, int out_dtype, void* C, int64_t
   RD_REQUIRE(!need_bias || bias, RD_ERR_ARG);
   RD_REQUIRE(!need_res || R, RD_ERR_ARG);
   RD_REQUIRE(epilogue != RD_EPI_SWIGLU || p->N % 2 == 0, RD_ERR_SIZE);
-  EpiArgs e{C, ldc, (const __nv_bfloat16*)bias, R, ldr};
+  EpiArgs e{};
+  e.C = C;
+  e.ldc = ldc;
+  e.bias = (const __nv_bfloat16*)bias;
+  e.R = R;
+  e.ldr = ldr;
   cudaStream_t s = (cudaStream_t)stream;
   return launch_epi(p, out_dtype, e, m_dev, epilogue, status, s);
+}
+
+extern "C" int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, void* q_out, void* k_cache, void* v_cache,
+                                        const int32_t* tok_row, const int32_t* tok_pos, const int32_t* tok_slot,
+                                        const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv, int hd,
+                                        int max_len, int32_t* status, void* stream) {
+  RD_REQUIRE(plan && q_out && k_cache && v_cache && tok_row && tok_pos && tok_slot && cos_table && sin_table, RD_ERR_ARG);
+  const GemmPlan* p = static_cast<const GemmPlan*>(plan);
+  RD_REQUIRE(hd == 128 && nh >= 1 && nkv >= 1 && n_pos >= 1 && max_len >= 1, RD_ERR_SIZE);
+  RD_REQUIRE(p->N == (nh + 2 * nkv) * hd, RD_ERR_SIZE);
+  RD_REQUIRE((((uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_table | (uintptr_t)sin_table) & 15) == 0,
+             RD_ERR_ALIGN);
+  EpiArgs e{};
+  e.C = q_out;  // unused by this epilogue; kept non-null for the common alignment checks in the kernel
+  e.ldc = (int64_t)nh * hd;
+  e.q_out = (__nv_bfloat16*)q_out;
+  e.k_cache = (__nv_bfloat16*)k_cache;
+  e.v_cache = (__nv_bfloat16*)v_cache;
+  e.tok_row = tok_row;
+  e.tok_pos = tok_pos;
+  e.tok_slot = tok_slot;
+  e.cos_t = cos_table;
+  e.sin_t = sin_table;
+  e.n_pos = n_pos;
+  e.nh = nh;
+  e.nkv = nkv;
+  e.max_len = max_len;
+  return launch_epi(p, RD_BF16, e, m_dev, kEpiQkvRope, status, (cudaStream_t)stream);
 }

@@ -13,6 +13,7 @@ Two entry points share one token-major implementation:
     or prefix-tree visibility; this is what the decode loop uses.
 """
 import math
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -48,6 +49,29 @@ class _Linear:
             and self.weight.data_ptr() % 16 == 0
         )
 
+    def _plan(self, a: torch.Tensor, lda: int, m_max: int) -> int:
+        n, k = self.weight.shape
+        key = (a.data_ptr(), lda, m_max)
+        plan = self._plans.get(key)
+        if plan is None:
+            plan = _lib.load().rd_gemm_plan_create(_lib.ptr(a), lda, m_max, _lib.ptr(self.weight), self.weight.stride(0), n, k)
+            if not plan:
+                raise _lib.RedrafterError("rd_gemm_plan_create failed (TMA descriptor could not be encoded)")
+            self._plans[key] = plan
+        return plan
+
+    def qkv_rope(self, a: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_row, tok_pos,
+                 tok_slot, cos: torch.Tensor, sin: torch.Tensor, nh: int, nkv: int, hd: int, m_dev, m_max: int,
+                 status: Optional[torch.Tensor]) -> None:
+        """This weight as the packed QKV projection with rotary embedding and cache append in the
+        GEMM epilogue (rd_gemm_bf16_tc_qkv_rope); tensor-core path only."""
+        if not self._tc_ok(a, a.stride(0)):
+            raise _lib.RedrafterError("the fused QKV projection needs the tensor-core GEMM path (bf16, aligned operands)")
+        plan = self._plan(a, a.stride(0), m_max)
+        _lib.call("rd_gemm_bf16_tc_qkv_rope", plan, _lib.ptr(m_dev), _lib.ptr(q_out), _lib.ptr(k_cache), _lib.ptr(v_cache),
+                  _lib.ptr(tok_row), _lib.ptr(tok_pos), _lib.ptr(tok_slot), _lib.ptr(cos), _lib.ptr(sin), cos.shape[0], nh, nkv,
+                  hd, k_cache.shape[2], _lib.ptr(status), _lib.stream())
+
     def __call__(self, a: torch.Tensor, c: torch.Tensor, epilogue: int = _lib.EPI_NONE, residual=None,
                  m_dev: Optional[torch.Tensor] = None, lda: Optional[int] = None, ldc: Optional[int] = None,
                  ldr: Optional[int] = None, m_max: Optional[int] = None, status: Optional[torch.Tensor] = None) -> None:
@@ -63,13 +87,7 @@ class _Linear:
             residual is None or (residual.data_ptr() % 16 == 0 and (ldr * esz) % 16 == 0)
         )
         if self._tc_ok(a, lda) and aligned:
-            key = (a.data_ptr(), lda, m_max)
-            plan = self._plans.get(key)
-            if plan is None:
-                plan = _lib.load().rd_gemm_plan_create(_lib.ptr(a), lda, m_max, _lib.ptr(self.weight), self.weight.stride(0), n, k)
-                if not plan:
-                    raise _lib.RedrafterError("rd_gemm_plan_create failed (TMA descriptor could not be encoded)")
-                self._plans[key] = plan
+            plan = self._plan(a, lda, m_max)
             _lib.call("rd_gemm_bf16_tc", plan, out_code, _lib.ptr(c), ldc, _lib.ptr(self.bias), _lib.ptr(residual),
                       ldr or 0, _lib.ptr(m_dev), epilogue, _lib.ptr(status), _lib.stream())
         else:
@@ -329,13 +347,20 @@ class LlamaForCausalLM(nn.Module):
         _lib.call("rd_embed_gather", code, _lib.ptr(self.model.embed_tokens.weight), _lib.ptr(tok_ids), _lib.ptr(h), m_max, md, H, st)
         dld_q = dense_mask.stride(1) if dense_mask is not None else 0
         dld_b = dense_mask.stride(0) if dense_mask is not None else 0
+        fused_rope = (self.dtype == torch.bfloat16 and hd == 128 and H % 64 == 0 and xn.data_ptr() % 16 == 0
+                      and os.environ.get("RD_FUSED_ROPE", "1") != "0")
         for l in range(self.n_layers):
             _lib.call("rd_rmsnorm", code, _lib.ptr(h), _lib.ptr(self.ln1[l]), _lib.ptr(xn), m_max, md, H, self.eps, st)
-            lin["qkv"][l](xn, qkv, _lib.EPI_NONE, m_dev=m_dev, m_max=m_max, status=self.gemm_status)
             kc, vc = cache_tensor[l, 0], cache_tensor[l, 1]
-            _lib.call("rd_rope_kv_write", code, _lib.ptr(qkv), _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(tok_row),
-                      _lib.ptr(tok_pos), _lib.ptr(tok_slot), _lib.ptr(cos), _lib.ptr(sin), cos.shape[0], m_max, md, nh, nkv,
-                      hd, max_len, st)
+            if fused_rope:
+                # rotary embedding and the cache append ride on the projection's epilogue
+                lin["qkv"][l].qkv_rope(xn, q, kc, vc, tok_row, tok_pos, tok_slot, cos, sin, nh, nkv, hd, m_dev, m_max,
+                                       self.gemm_status)
+            else:
+                lin["qkv"][l](xn, qkv, _lib.EPI_NONE, m_dev=m_dev, m_max=m_max, status=self.gemm_status)
+                _lib.call("rd_rope_kv_write", code, _lib.ptr(qkv), _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(tok_row),
+                          _lib.ptr(tok_pos), _lib.ptr(tok_slot), _lib.ptr(cos), _lib.ptr(sin), cos.shape[0], m_max, md, nh, nkv,
+                          hd, max_len, st)
             self._attention(code, q, kc, vc, attn, row_start, kv_begin, base_len, batch, m_max, max_new, max_kv, mode, tree_mask,
                             mask_words, dense_mask, dld_q, dld_b, st)
             lin["o"][l](attn, h, _lib.EPI_RES, residual=h, m_dev=m_dev, m_max=m_max, status=self.gemm_status)

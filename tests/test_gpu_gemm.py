@@ -127,3 +127,45 @@ def test_gemm_tc_strided_output():
     want = torch.nn.functional.silu(a.float() @ w.float().T + b.float())
     assert torch.all(x[:, :H] == 0)
     assert (x[:, H:].float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+
+
+def test_qkv_projection_with_fused_rope_equals_projection_then_rope():
+    """rd_gemm_bf16_tc_qkv_rope against rd_gemm_bf16_tc + rd_rope_kv_write on the same inputs: rotated
+    Q rows, rotated K and plain V rows at the tokens' cache slots, bit for bit (GQA, ragged rows,
+    a live count below the capacity, positions beyond the table clamped)."""
+    from recurrent_drafting import _lib
+    from recurrent_drafting.modeling_llama import _Linear, rope_tables
+
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(3)
+    B, nh, nkv, hd, H, max_len, n_pos = 3, 8, 2, 128, 512, 300, 256
+    m_max, live = 700, 613
+    xn = (torch.randn(m_max, H, generator=g, device=dev) * 0.5).bfloat16()
+    w = (torch.randn((nh + 2 * nkv) * hd, H, generator=g, device=dev) * 0.1).bfloat16()
+    tok_row = torch.randint(0, B, (m_max,), generator=g, device=dev, dtype=torch.int32)
+    tok_slot = torch.empty(m_max, dtype=torch.int32, device=dev)
+    for b in range(B):  # distinct slots per row
+        idx = (tok_row == b).nonzero().flatten()
+        tok_slot[idx] = torch.randperm(max_len, generator=g, device=dev)[: idx.numel()].to(torch.int32)
+    tok_pos = torch.randint(0, n_pos + 20, (m_max,), generator=g, device=dev, dtype=torch.int32)
+    cos, sin = rope_tables(hd, n_pos, 10000.0, dev)
+    m_dev = torch.tensor([live], dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    lin = _Linear(w)
+    # separate kernels
+    qkv = torch.zeros(m_max, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, device=dev)
+    q1 = torch.full((m_max, nh * hd), 5.0, dtype=torch.bfloat16, device=dev)
+    k1 = torch.full((B, nkv, max_len, hd), 6.0, dtype=torch.bfloat16, device=dev)
+    v1 = torch.full((B, nkv, max_len, hd), 7.0, dtype=torch.bfloat16, device=dev)
+    lin(xn, qkv, _lib.EPI_NONE, m_dev=m_dev, status=status)
+    _lib.call("rd_rope_kv_write", _lib.BF16, _lib.ptr(qkv), _lib.ptr(q1), _lib.ptr(k1), _lib.ptr(v1), _lib.ptr(tok_row),
+              _lib.ptr(tok_pos), _lib.ptr(tok_slot), _lib.ptr(cos), _lib.ptr(sin), n_pos, m_max, _lib.ptr(m_dev), nh, nkv, hd,
+              max_len, _lib.stream())
+    # fused
+    q2, k2, v2 = torch.full_like(q1, 5.0), torch.full_like(k1, 6.0), torch.full_like(v1, 7.0)
+    lin.qkv_rope(xn, q2, k2, v2, tok_row, tok_pos, tok_slot, cos, sin, nh, nkv, hd, m_dev, m_max, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(q1, q2) and torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.all(q2[live:] == 5.0), "rows beyond the live count were written"
+    assert (q2[:live] != 5.0).any() and (k2 != 6.0).any() and (v2 != 7.0).any()
