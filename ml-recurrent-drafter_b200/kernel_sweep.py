@@ -192,6 +192,7 @@ def main() -> None:
     ap.add_argument("--quick", action="store_true", help="corner cells only")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--out", default=None, help="write the markdown table here as well")
+    ap.add_argument("--cell", type=int, nargs=4, metavar=("B", "W", "LB", "S"), default=None, help="run this one cell only")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("kernel_sweep needs a CUDA device")
@@ -202,6 +203,8 @@ def main() -> None:
     Bs, Ws, Ls, Ss = [1, 8, 64], [8, 45, 64], [3, 5, 7], [512, 2048, 4096]
     if args.quick:
         Bs, Ws, Ls, Ss = [1, 64], [8, 64], [3, 7], [512, 4096]
+    if args.cell:
+        Bs, Ws, Ls, Ss = [[x] for x in args.cell]
     timer = Timer(args.reps)
     cols = ["B", "W", "Lb", "S", "tokens", "shared_prefix_fraction", "mean_accepted", "pack_us", "attn_shares", "attn_us", "attn_gbs",
             "attn_frac_hbm", "attn_tflops", "argmax_us", "argmax_gbs", "argmax_frac_hbm", "commit_layers", "commit_us", "commit_gbs"]
