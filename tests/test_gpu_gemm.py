@@ -104,6 +104,9 @@ def test_gemm_tc_shapes(M, N, K, live):
         (1800, 13000, 256, 1800, "bias_silu_res", torch.bfloat16),  # ragged last tile, second half of it empty
         (400, 40000, 128, None, "res", torch.float32),
         (1800, 32000, 256, 17, "bias", torch.float32),  # one short chunk
+        (1800, 15360, 5120, 1100, "none", torch.bfloat16),  # 13B-architecture shapes: QKV,
+        (1800, 27648, 5120, 900, "swiglu", torch.bfloat16),  # gate/up,
+        (1800, 5120, 13824, 800, "res", torch.bfloat16),  # down projection
     ],
 )
 def test_gemm_tc_large_n(M, N, K, live, epi, out_dtype):
