@@ -64,10 +64,11 @@ class _DecodeState:
         H = llm.config.hidden_size
         i32 = dict(dtype=torch.int32, device=device)
         self.kv_begin = torch.zeros(B, **i32)
-        self.small = torch.zeros(2, B, **i32)  # row 0: kv_len, row 1: n_accepted (one read-back per step)
+        # row 0: kv_len, row 1: n_accepted, row 2 [0]: status word of the tensor-core kernels (one read-back per step)
+        self.small = torch.zeros(3, B, **i32)
         self.kv_len = self.small[0]
         self.n_accepted = self.small[1]
-        self.small_host = torch.zeros(2, B, dtype=torch.int32).pin_memory()
+        self.small_host = torch.zeros(3, B, dtype=torch.int32).pin_memory()
         self.seq_in_beam = torch.zeros(B, **i32)
         self.token_buf = torch.zeros(B, max_len, dtype=torch.int64, device=device)
         self.ctx = torch.zeros(B, H, dtype=llm.dtype, device=device)
@@ -75,7 +76,7 @@ class _DecodeState:
         self.llm_tok = torch.zeros(B * W * Lb, **i32)
         self.fp = tree_attention.alloc_flat(B, W, Lb, device)
         self.p = modeling_drafter.new_sparse(B * W * Lb, device)
-        self.status = torch.zeros(1, **i32)
+        self.status = self.small[2, :1]
 
 
 class RecurrentDrafting(torch.nn.Module):
@@ -219,6 +220,9 @@ class RecurrentDrafting(torch.nn.Module):
                 self._step(st, cache, beam_shape, sampling_args, s_max, rec)
                 st.small_host.copy_(st.small, non_blocking=True)
                 torch.cuda.current_stream().synchronize()
+                if int(st.small_host[2, 0]) != 0:
+                    raise _lib.RedrafterError(
+                        f"a tensor-core kernel gave up waiting on its pipeline (status {int(st.small_host[2, 0])})")
                 s_max = int(st.small_host[0].max())
                 out = torch.empty(B, s_max + 1, dtype=torch.int64, device=dev)
                 _lib.call("rd_emit_tokens", _lib.ptr(st.token_buf), st.token_buf.shape[1], _lib.ptr(st.kv_begin),
