@@ -175,6 +175,13 @@ RD_API int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, void
                              const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv, int hd,
                              int max_len, int32_t* status, void* stream);
 
+/* Measurement aid: with acc != NULL (two 64-bit device counters, zeroed by the caller) every
+ * rd_gemm_bf16_tc* launch adds to acc[0] the nanoseconds its first CTA spent between the end of its
+ * dependency wait and its last tile (%globaltimer) and to acc[1] the launch's 2*M*N*K, M read on
+ * the device.  acc = NULL switches it off (the default).  A cudaMemcpyToSymbol: call it while no
+ * GEMM of this library is running. */
+RD_API int rd_gemm_set_timing(void* acc);
+
 /* ---------------------------------------------------------------------------------------------
  * Llama verify forward pieces (recurrent_drafting/modeling_llama.py). */
 

@@ -42,6 +42,12 @@ static int g_use_pairs = [] {
   return (v && v[0] == '0') ? 0 : 1;
 }();
 
+// Optional in-kernel timing (rd_gemm_set_timing): acc[0] += nanoseconds CTA 0 spent between its
+// dependency wait and its last tile, acc[1] += 2*M*N*K of the launch.  CTA (pair) 0 owns the largest
+// share of the tiles, so its lifetime is the kernel's duration without launch latency and without
+// the perturbation of event records between dependent launches.
+__device__ unsigned long long* g_gemm_timing = nullptr;
+
 struct GemmPlan {
   CUtensorMap map_a;  // activations [m_max, K], box 64 x 128
   CUtensorMap map_w;  // weights [N, K], box 64 x 128
@@ -460,6 +466,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   // count, the activations, the output) is valid once the kernels before this one have finished
   rd::pdl_wait();
   const int M = rd::live_rows(m_dev, m_max);
+  unsigned long long* const timing = (blockIdx.x == 0 && threadIdx.x == 0) ? g_gemm_timing : nullptr;
+  const uint64_t t_begin = timing ? global_ns() : 0;
   const int w_tiles = (N + BM - 1) / BM;
   const Chunking ch = make_chunking(M, w_tiles, gridDim.x);
   const int total_tiles = M > 0 ? w_tiles * ch.n_chunks : 0;
@@ -597,6 +605,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   tc_fence_before();
   __syncthreads();
+  if (timing) {
+    atomicAdd(timing, (unsigned long long)(global_ns() - t_begin));
+    atomicAdd(timing + 1, 2ull * (unsigned long long)M * (unsigned long long)N * (unsigned long long)K);
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kMaxChunk) : "memory");
@@ -724,6 +736,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = *tmem_slot;
   rd::pdl_wait();  // global memory is valid once the kernels before this one have finished
   const int M = rd::live_rows(m_dev, m_max);
+  unsigned long long* const timing = (blockIdx.x == 0 && threadIdx.x == 0) ? g_gemm_timing : nullptr;
+  const uint64_t t_begin = timing ? global_ns() : 0;
   const int w_pairs = (N + 2 * BM - 1) / (2 * BM);
   const Chunking ch = make_chunking(M, w_pairs, n_pairs);
   const int total_tiles = M > 0 ? w_pairs * ch.n_chunks : 0;
@@ -865,6 +879,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   // MMAs of the pair are in flight: meet at a cluster barrier first.
   tc_fence_before();
   __syncthreads();
+  if (timing) {
+    atomicAdd(timing, (unsigned long long)(global_ns() - t_begin));
+    atomicAdd(timing + 1, 2ull * (unsigned long long)M * (unsigned long long)N * (unsigned long long)K);
+  }
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
@@ -1036,4 +1054,14 @@ extern "C" int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, 
   e.nkv = nkv;
   e.max_len = max_len;
   return launch_epi(p, RD_BF16, e, m_dev, kEpiQkvRope, status, (cudaStream_t)stream);
+}
+
+extern "C" int rd_gemm_set_timing(void* acc) {
+  unsigned long long* p = static_cast<unsigned long long*>(acc);
+  cudaError_t err = cudaMemcpyToSymbol(g_gemm_timing, &p, sizeof(p));
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
+  return RD_OK;
 }

@@ -39,6 +39,7 @@ SIGNATURES = {
     "rd_gemm_plan_destroy": (None, [_P]),
     "rd_gemm_bf16_tc": (_I, [_P, _I, _P, _L, _P, _P, _L, _P, _I, _P, _P]),
     "rd_gemm_bf16_tc_qkv_rope": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
+    "rd_gemm_set_timing": (_I, [_P]),
     "rd_embed_gather": (_I, [_I, _P, _P, _P, _I, _P, _I, _P]),
     "rd_rmsnorm": (_I, [_I, _P, _P, _P, _I, _P, _I, _F, _P]),
     "rd_rope_kv_write": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P]),
