@@ -110,3 +110,30 @@ def test_cpu_input_is_rejected():
     model = rd.RecurrentDrafting(llm, dr)
     with pytest.raises(rd._lib.RedrafterError):
         next(model.generate(rd.stats.Ledger(), torch.zeros(1, 4, dtype=torch.long), 8, rd.modeling_drafter.BeamShape(2, 2)))
+
+
+def test_generation_stops_when_every_row_has_produced_eos(g_model):
+    """The whole-batch EOS test of the loop (recurrent_drafting.py:697-705): generation ends with the
+    step in which the last row has emitted the EOS id, not earlier and not later; same stream as
+    the oracle run with the same EOS id."""
+    import recurrent_drafting as rd
+
+    B, Lp, gen, W, L = (int(x) for x in g_model["gen_c1_shape"])
+    llm, dr, lw, dw = build_models(mb.C1_LLAMA, mb.C1_DRAFTER, 123)
+    model = rd.RecurrentDrafting(llm, dr)
+    prompt = g_model["gen_c1_prompt"]
+    final = g_model["gen_c1_final"]
+    # an id that every row emits at some point of the unconstrained run, as late as possible
+    tail = final[:, Lp:]
+    common = set(tail[0].tolist())
+    for b in range(1, B):
+        common &= set(tail[b].tolist())
+    assert common, "the fixture rows share no generated token"
+    eos = max(common, key=lambda tok: max(int(np.argmax(tail[b] == tok)) for b in range(B)))
+    want = list(ogen.generate(lw, mb.C1_LLAMA, dw, mb.C1_DRAFTER["num_draft_layers"], prompt, Lp + gen, W, L, greedy=True,
+                              eos_token_id=int(eos)))
+    got = [o.cpu().numpy() for o in model.generate(rd.stats.Ledger(), t(prompt), Lp + gen, rd.modeling_drafter.BeamShape(W, L),
+                                                   rd.SamplingArgs(1.0, True), rd.SpecialTokens(0, int(eos)))]
+    assert len(got) == len(want) and len(got) < len(g_model["gen_c1_lengths"])
+    for a, b_ in zip(got, want):
+        assert np.array_equal(a, b_)

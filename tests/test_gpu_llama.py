@@ -156,7 +156,7 @@ def test_state_dict_round_trip():
 
 
 @pytest.mark.parametrize("mode", ["causal", "tree"])
-@pytest.mark.parametrize("W,L,bases", [(45, 5, (10, 70, 133)), (8, 3, (0, 1, 64)), (64, 7, (300, 5, 129))])
+@pytest.mark.parametrize("W,L,bases", [(45, 5, (10, 70, 133)), (8, 3, (0, 1, 64)), (64, 7, (300, 5, 129)), (64, 8, (0, 63, 200))])
 def test_attention_tcgen05(mode, W, L, bases):
     """The tcgen05 attention (TMA + TMEM) against the fp32 oracle: ragged rows, several query tiles
     (n_new > 128), prefixes that end inside, at and before a key-tile boundary, GQA."""
