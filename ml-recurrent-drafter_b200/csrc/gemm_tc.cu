@@ -214,7 +214,7 @@ constexpr int kScrLd = 36;  // floats per scratch row: 16-byte aligned rows, con
 
 // Element-wise part of the epilogue in accumulator layout (lane = output feature n, i = token).
 template <int EPI>
-__device__ __forceinline__ void epilogue_math(float* v, const EpiArgs& e, int n, int N) {
+__device__ __forceinline__ void epilogue_math(float* v, const EpiArgs& e, int n, int N, bool swiglu_here) {
   if (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) {
     const float bias = n < N ? __bfloat162float(e.bias[n]) : 0.f;
 #pragma unroll
@@ -224,7 +224,8 @@ __device__ __forceinline__ void epilogue_math(float* v, const EpiArgs& e, int n,
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = rd::silu_f(v[i]);
   }
-  if (EPI == RD_EPI_SWIGLU) {
+  if (EPI == RD_EPI_SWIGLU && swiglu_here) {
+    // feature-per-lane stores only (the vector path forms the product after the transpose):
     // weight rows (2i, 2i+1) = (gate_i, up_i) sit in adjacent lanes; even lanes keep the product
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -300,24 +301,27 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
     return;
   }
   // transpose: scr[token i][feature]
-  if (EPI == RD_EPI_SWIGLU) {
-    if ((lane & 1) == 0) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) scr[i * kScrLd + (lane >> 1)] = v[i];
+  for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = v[i];
+  __syncwarp();
+  float o[kOut];
+  if (EPI == RD_EPI_SWIGLU) {
+    // the token's 32 features are 16 (gate, up) pairs: one SiLU per output, no lane exchange
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 f = *reinterpret_cast<const float4*>(scr + lane * kScrLd + 4 * j);
+      o[2 * j] = rd::silu_f(f.x) * f.y;
+      o[2 * j + 1] = rd::silu_f(f.z) * f.w;
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = v[i];
-  }
-  __syncwarp();
-  float o[kOut];
-#pragma unroll
-  for (int j = 0; j < kOut / 4; ++j) {
-    const float4 f = *reinterpret_cast<const float4*>(scr + lane * kScrLd + 4 * j);
-    o[4 * j] = f.x;
-    o[4 * j + 1] = f.y;
-    o[4 * j + 2] = f.z;
-    o[4 * j + 3] = f.w;
+    for (int j = 0; j < kOut / 4; ++j) {
+      const float4 f = *reinterpret_cast<const float4*>(scr + lane * kScrLd + 4 * j);
+      o[4 * j] = f.x;
+      o[4 * j + 1] = f.y;
+      o[4 * j + 2] = f.z;
+      o[4 * j + 3] = f.w;
+    }
   }
   __syncwarp();  // the scratch is reused by the next block
   const int tok = tok0 + lane;
@@ -592,7 +596,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (EPI == kEpiQkvRope) {
           epilogue_rope_block(v, epi, scratch, quarter, lane, (n_warp0 - quarter * 32) / 128, tok_base + c, tok_limit);
         } else {
-          epilogue_math<EPI>(v, epi, n_warp0 + lane, N);
+          epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok);
           epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
         }
       }
@@ -864,7 +868,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (EPI == kEpiQkvRope) {
           epilogue_rope_block(v, epi, scratch, quarter, lane, (n_warp0 - quarter * 32) / 128, tok_base + c, tok_limit);
         } else {
-          epilogue_math<EPI>(v, epi, n_warp0 + lane, N);
+          epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok);
           epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
         }
       }
