@@ -148,6 +148,23 @@ class Drafter(torch.nn.Module):
         self._invalidate()
         return self
 
+    @classmethod
+    def from_pretrained(cls, path: str, torch_dtype: torch.dtype = torch.bfloat16, device="cuda") -> "Drafter":
+        """A drafter checkpoint directory as written by the reference's training code (config.json of
+        model_type recurrent_drafting_drafter + weights under the reference's parameter names)."""
+        from . import checkpoint
+
+        cfg = configuration_drafter.DrafterConfig.from_pretrained(path)
+        model = cls(cfg)
+        ck = checkpoint.LazyCheckpoint(path)
+        model.load_state_dict({k: ck.pop(k) for k in ck.keys()})
+        return model.to(device=device, dtype=torch_dtype)
+
+    def save_pretrained(self, path: str) -> None:
+        from . import checkpoint
+
+        checkpoint.save_directory(path, self.config, self.state_dict())
+
     def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
         out = super().load_state_dict(state_dict, strict=strict)
         self._invalidate()

@@ -20,7 +20,7 @@ import torch
 from torch import nn
 from transformers.modeling_outputs import CausalLMOutput
 
-from . import _lib, attention, kv_cache
+from . import _lib, attention, checkpoint, kv_cache
 
 
 class _Linear:
@@ -189,7 +189,7 @@ class LlamaForCausalLM(nn.Module):
 
     def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
         """Accepts the HF / reference names and packs them into the kernel layouts."""
-        sd = dict(state_dict)
+        sd = state_dict if isinstance(state_dict, checkpoint.LazyCheckpoint) else dict(state_dict)
         if any(k.startswith("wqkv.") for k in sd):
             out = super().load_state_dict(sd, strict=strict)
             self._invalidate()
@@ -216,6 +216,26 @@ class LlamaForCausalLM(nn.Module):
             raise KeyError(f"unexpected keys in state dict: {leftover[:5]}")
         self._invalidate()
         return leftover
+
+    @classmethod
+    def from_pretrained(cls, path: str, torch_dtype: torch.dtype = torch.bfloat16, device="cuda") -> "LlamaForCausalLM":
+        """A Hugging Face Llama checkpoint directory (config.json + safetensors / bin shards with the HF
+        names), packed into the kernel layouts tensor by tensor (cmd/generate.py:55-63)."""
+        import transformers
+
+        cfg = transformers.LlamaConfig.from_pretrained(path)
+        if getattr(cfg, "rope_theta", None) is None:
+            cfg.rope_theta = float((getattr(cfg, "rope_parameters", None) or {}).get("rope_theta", 10000.0))
+        model = cls(cfg).to(device=device, dtype=torch_dtype)
+        ck = checkpoint.LazyCheckpoint(path)
+        if "lm_head.weight" not in ck and getattr(cfg, "tie_word_embeddings", False):
+            raise _lib.RedrafterError("checkpoints with tied input/output embeddings are not supported")
+        model.load_state_dict(ck)
+        return model
+
+    def save_pretrained(self, path: str) -> None:
+        """config.json + model.safetensors with the HF names."""
+        checkpoint.save_directory(path, self.config, self.reference_state_dict())
 
     def reference_state_dict(self) -> Dict[str, torch.Tensor]:
         """The weights under the HF / reference names."""
