@@ -340,7 +340,9 @@ def model_cases(rd, out):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of apple/ml-recurrent-drafter>")
+    ref_root = sys.argv[1]
     _install_shims(ref_root)
     import recurrent_drafting as rd
 
