@@ -3,21 +3,25 @@
 // One CTA serves 128 queries of one (batch row, head): normally every packed tree token of the row.
 //   warps 0, 6  TMA producers (one elected lane each): warp 0 loads the Q tile once and then the K
 //               tiles of 64 keys, warp 6 the V tiles (two 64-column boxes each, 128-byte swizzle, no
-//               multicast), each into its own two-stage ring: a K stage is released as soon as QK^T of its tile is done,
-//               a V stage after PV, so the K loads run well ahead of the V loads;
+//               multicast), each into its own two-stage ring.  A K stage is free as soon as QK^T of
+//               its tile is done, a V stage after PV; the producers wait on the same completion
+//               barriers the softmax uses (one commit per product);
 //   warp 1      MMA issuer (one elected thread):
 //                 S = Q K^T   tcgen05.mma, A = Q and B = K from shared memory (both K-major),
 //                             accumulator S[128 x 64] in TMEM;
 //                 O_t = P V   tcgen05.mma, A = P (bf16) read from TMEM, B = V from shared memory as
 //                             an MN-major operand (V rows are keys, head_dim contiguous);
-//   warps 2-5   softmax: thread r owns query row r (= TMEM lane r): tcgen05.ld of its S row,
-//               scale + visibility (cached prefix, causal or prefix-tree bitmask), running max and
-//               sum in the exp2 domain, P written back to TMEM with tcgen05.st.  O accumulates in
-//               TMEM across tiles; a warp rescales its O rows (tcgen05.ld / st) only on the tiles
-//               where one of its rows' running max actually moved.
+//   warps 2-5   softmax: thread r owns query row r (= TMEM lane r): tcgen05.ld of its S row, one
+//               64-bit visibility word per tile (cached prefix, causal or prefix-tree bitmask), a
+//               running max that only moves when exceeded by more than 2^6, p = 2^(s*c - m*c) by one
+//               FFMA + ex2.approx, P written back to TMEM with tcgen05.st.  O accumulates in TMEM
+//               across tiles; a warp rescales its O rows (tcgen05.ld / st) only on the tiles where
+//               one of its rows' running max moved.
 // QK of tile t+1 overlaps the softmax and PV of tile t; P is double-buffered in TMEM so that the
-// softmax of tile t never waits for PV of tile t-1; two CTAs fit on an SM (96 KB of shared memory,
-// 256 TMEM columns each) and overlap each other's latencies.
+// softmax of tile t does not wait for PV of tile t-1 before writing P; two CTAs fit on an SM (105 KB
+// of shared memory, 256 TMEM columns each) and overlap each other's latencies.  With n_split > 1
+// a CTA walks only its share of the key tiles and leaves an unnormalised partial for the merge
+// kernel at the end of this file.
 //
 // Every mbarrier wait is bounded; on give-up the kernel records a code in *status, stops issuing,
 // lets outstanding bulk copies land, frees its TMEM and returns.
