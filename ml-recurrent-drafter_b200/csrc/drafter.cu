@@ -10,26 +10,30 @@ namespace {
 template <typename T>
 __global__ void drafter_prepare_kernel(const T* __restrict__ embed, const int64_t* __restrict__ beams,
                                        const int32_t* __restrict__ parent, const T* __restrict__ ctx, T* __restrict__ a,
-                                       T* __restrict__ x, int W, int Lb, int H, int k) {
+                                       T* __restrict__ x, int W, int Lb, int H, int k, int vec) {
   const int r = blockIdx.x;
   const int b = r / W;
   const int64_t tok = beams[(int64_t)r * Lb + k];
   const T* e = embed + tok * (int64_t)H;
   T* arow = a + (int64_t)r * 2 * H;
   T* xrow = x + (int64_t)r * 2 * H;
-  if (k == 0) {
-    const T* c = ctx + (int64_t)b * H;
-    for (int d = threadIdx.x; d < H; d += blockDim.x) {
-      arow[d] = e[d];
-      arow[H + d] = rd::Num<T>::from_f(0.f);
-      xrow[d] = c[d];
+  const T* c = ctx + (int64_t)b * H;
+  const T* s = (k == 0) ? nullptr : x + ((int64_t)b * W + parent[r]) * 2 * H + H;
+  constexpr int VEC = 16 / sizeof(T);
+  if (vec) {
+    // 16-byte copies: a = [embedding(token), parent state or zeros]; x[:H] = context (first iteration only)
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int d = threadIdx.x; d < H / VEC; d += blockDim.x) {
+      reinterpret_cast<uint4*>(arow)[d] = reinterpret_cast<const uint4*>(e)[d];
+      reinterpret_cast<uint4*>(arow + H)[d] = s ? reinterpret_cast<const uint4*>(s)[d] : zero;
+      if (k == 0) reinterpret_cast<uint4*>(xrow)[d] = reinterpret_cast<const uint4*>(c)[d];
     }
-  } else {
-    const T* s = x + ((int64_t)b * W + parent[r]) * 2 * H + H;
-    for (int d = threadIdx.x; d < H; d += blockDim.x) {
-      arow[d] = e[d];
-      arow[H + d] = s[d];
-    }
+    return;
+  }
+  for (int d = threadIdx.x; d < H; d += blockDim.x) {
+    arow[d] = e[d];
+    arow[H + d] = s ? s[d] : rd::Num<T>::from_f(0.f);
+    if (k == 0) xrow[d] = c[d];
   }
 }
 
@@ -490,13 +494,15 @@ extern "C" int rd_drafter_prepare(int dtype, const void* embed, const int64_t* b
                  k < Lb - 1,
              RD_ERR_SIZE);
   cudaStream_t s = (cudaStream_t)stream;
+  const int esz = dtype == RD_F32 ? 4 : 2;
+  const int vec = ((H * esz) % 16 == 0) && ((((uintptr_t)embed | (uintptr_t)ctx | (uintptr_t)a | (uintptr_t)x) & 15) == 0);
   if (dtype == RD_F32)
     drafter_prepare_kernel<float><<<B * W, 256, 0, s>>>((const float*)embed, beams, parent, (const float*)ctx,
-                                                         (float*)a, (float*)x, W, Lb, H, k);
+                                                         (float*)a, (float*)x, W, Lb, H, k, vec);
   else if (dtype == RD_BF16)
     drafter_prepare_kernel<__nv_bfloat16><<<B * W, 256, 0, s>>>((const __nv_bfloat16*)embed, beams, parent,
                                                                  (const __nv_bfloat16*)ctx, (__nv_bfloat16*)a,
-                                                                 (__nv_bfloat16*)x, W, Lb, H, k);
+                                                                 (__nv_bfloat16*)x, W, Lb, H, k, vec);
   else
     return RD_ERR_DTYPE;
   RD_CHECK_LAUNCH();
