@@ -7,11 +7,16 @@ namespace {
 
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int64_t* __restrict__ ids, T* __restrict__ out,
-                                    int m_max, const int32_t* __restrict__ m_dev, int H) {
+                                    int m_max, const int32_t* __restrict__ m_dev, int H, int vec) {
   const int t = blockIdx.x;
   if (t >= rd::live_rows(m_dev, m_max)) return;
   const T* src = table + ids[t] * (int64_t)H;
   T* dst = out + (int64_t)t * H;
+  constexpr int VEC = 16 / sizeof(T);
+  if (vec) {
+    for (int d = threadIdx.x; d < H / VEC; d += blockDim.x) reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(src)[d];
+    return;
+  }
   for (int d = threadIdx.x; d < H; d += blockDim.x) dst[d] = src[d];
 }
 
@@ -266,7 +271,9 @@ extern "C" int rd_embed_gather(int dtype, const void* table, const int64_t* ids,
   RD_REQUIRE(table && ids && out, RD_ERR_ARG);
   RD_REQUIRE(m_max >= 1 && H >= 1, RD_ERR_SIZE);
   cudaStream_t s = (cudaStream_t)stream;
-  RD_DISPATCH_T(dtype, (embed_gather_kernel<T><<<m_max, 256, 0, s>>>((const T*)table, ids, (T*)out, m_max, m_dev, H)));
+  const int esz = dtype == RD_F32 ? 4 : 2;
+  const int vec = ((H * esz) % 16 == 0) && ((((uintptr_t)table | (uintptr_t)out) & 15) == 0);
+  RD_DISPATCH_T(dtype, (embed_gather_kernel<T><<<m_max, 256, 0, s>>>((const T*)table, ids, (T*)out, m_max, m_dev, H, vec)));
   RD_CHECK_LAUNCH();
   return RD_OK;
 }
