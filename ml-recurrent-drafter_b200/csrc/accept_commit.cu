@@ -64,6 +64,8 @@ struct CommitArgs {
 
 template <typename T, bool SAMPLE>
 __global__ void __launch_bounds__(kThreads) accept_commit_kernel(CommitArgs a) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   const int plane = (int)blockIdx.x - 1;  // layer*2 + kv; -1 = the block that writes the row outputs
   const int b = blockIdx.y;
   const int W = a.W, Lb = a.Lb;
@@ -236,16 +238,20 @@ int check_common(const CommitArgs& a) {
 template <bool SAMPLE>
 int launch(int dtype, const CommitArgs& a, cudaStream_t s) {
   dim3 grid(a.NL * 2 + 1, a.B);
+  cudaError_t err = cudaSuccess;
   if (dtype == RD_F32) {
     RD_REQUIRE(a.NL == 0 || (a.hd * 4) % 16 == 0, RD_ERR_ALIGN);
-    accept_commit_kernel<float, SAMPLE><<<grid, kThreads, 0, s>>>(a);
+    err = rd::launch_chained(accept_commit_kernel<float, SAMPLE>, grid, dim3(kThreads), 0, s, 1, a);
   } else if (dtype == RD_BF16) {
     RD_REQUIRE(a.NL == 0 || (a.hd * 2) % 16 == 0, RD_ERR_ALIGN);
-    accept_commit_kernel<__nv_bfloat16, SAMPLE><<<grid, kThreads, 0, s>>>(a);
+    err = rd::launch_chained(accept_commit_kernel<__nv_bfloat16, SAMPLE>, grid, dim3(kThreads), 0, s, 1, a);
   } else {
     return RD_ERR_DTYPE;
   }
-  RD_CHECK_LAUNCH();
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 

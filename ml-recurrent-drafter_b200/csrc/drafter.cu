@@ -11,6 +11,8 @@ template <typename T>
 __global__ void drafter_prepare_kernel(const T* __restrict__ embed, const int64_t* __restrict__ beams,
                                        const int32_t* __restrict__ parent, const T* __restrict__ ctx, T* __restrict__ a,
                                        T* __restrict__ x, int W, int Lb, int H, int k, int vec) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   const int r = blockIdx.x;
   const int b = r / W;
   const int64_t tok = beams[(int64_t)r * Lb + k];
@@ -192,6 +194,8 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
     const T* __restrict__ logits, int64_t ld, int rows_max, const int32_t* __restrict__ rows_dev, int V, int top_k,
     float mask_value, int subtract_max, float temperature, int vec_ok, float* __restrict__ kept_val,
     int32_t* __restrict__ kept_idx, int32_t* __restrict__ kept_cnt, float* __restrict__ masked_logp) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   const int row_id = blockIdx.x;
   if (row_id >= rd::live_rows(rows_dev, rows_max)) return;
   __shared__ TopkShared sh;
@@ -357,6 +361,8 @@ __global__ void __launch_bounds__(kSelThreads) beam_select_kernel(
     const int32_t* __restrict__ kept_cnt, const float* __restrict__ score_in, float* __restrict__ score_out,
     const int64_t* __restrict__ beams_in, int64_t* __restrict__ beams_out, const int32_t* __restrict__ anc_in,
     int32_t* __restrict__ anc_out, int32_t* __restrict__ parent_out) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   const int b = blockIdx.x;
   extern __shared__ unsigned char raw[];
   float* cs = reinterpret_cast<float*>(raw);  // [W][W] candidate scores, row w = beam w's list
@@ -496,16 +502,19 @@ extern "C" int rd_drafter_prepare(int dtype, const void* embed, const int64_t* b
   cudaStream_t s = (cudaStream_t)stream;
   const int esz = dtype == RD_F32 ? 4 : 2;
   const int vec = ((H * esz) % 16 == 0) && ((((uintptr_t)embed | (uintptr_t)ctx | (uintptr_t)a | (uintptr_t)x) & 15) == 0);
+  cudaError_t err = cudaSuccess;
   if (dtype == RD_F32)
-    drafter_prepare_kernel<float><<<B * W, 256, 0, s>>>((const float*)embed, beams, parent, (const float*)ctx,
-                                                         (float*)a, (float*)x, W, Lb, H, k, vec);
+    err = rd::launch_chained(drafter_prepare_kernel<float>, dim3(B * W), dim3(256), 0, s, 1, (const float*)embed, beams, parent,
+                             (const float*)ctx, (float*)a, (float*)x, W, Lb, H, k, vec);
   else if (dtype == RD_BF16)
-    drafter_prepare_kernel<__nv_bfloat16><<<B * W, 256, 0, s>>>((const __nv_bfloat16*)embed, beams, parent,
-                                                                 (const __nv_bfloat16*)ctx, (__nv_bfloat16*)a,
-                                                                 (__nv_bfloat16*)x, W, Lb, H, k, vec);
+    err = rd::launch_chained(drafter_prepare_kernel<__nv_bfloat16>, dim3(B * W), dim3(256), 0, s, 1, (const __nv_bfloat16*)embed,
+                             beams, parent, (const __nv_bfloat16*)ctx, (__nv_bfloat16*)a, (__nv_bfloat16*)x, W, Lb, H, k, vec);
   else
     return RD_ERR_DTYPE;
-  RD_CHECK_LAUNCH();
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 
@@ -516,20 +525,24 @@ extern "C" int rd_vocab_topk(int logits_dtype, const void* logits, int64_t ld, i
   RD_REQUIRE(rows_max >= 1 && V >= 1 && top_k >= 1 && top_k <= RD_TOPK_MAX_KEPT && ld >= V, RD_ERR_SIZE);
   RD_REQUIRE(temperature > 0.f, RD_ERR_ARG);
   cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t err = cudaSuccess;
   if (logits_dtype == RD_F32) {
     const int vec_ok = ((uintptr_t)logits % 16 == 0) && ((ld * 4) % 16 == 0);
-    vocab_topk_kernel<float><<<rows_max, kTopkThreads, 0, s>>>((const float*)logits, ld, rows_max, rows_dev, V, top_k, mask_value,
-                                                               subtract_max, temperature, vec_ok, kept_val, kept_idx, kept_cnt,
-                                                               masked_logp);
+    err = rd::launch_chained(vocab_topk_kernel<float>, dim3(rows_max), dim3(kTopkThreads), 0, s, 1, (const float*)logits, ld, rows_max,
+                             rows_dev, V, top_k, mask_value, subtract_max, temperature, vec_ok, kept_val, kept_idx, kept_cnt,
+                             masked_logp);
   } else if (logits_dtype == RD_BF16) {
     const int vec_ok = ((uintptr_t)logits % 16 == 0) && ((ld * 2) % 16 == 0);
-    vocab_topk_kernel<__nv_bfloat16><<<rows_max, kTopkThreads, 0, s>>>((const __nv_bfloat16*)logits, ld, rows_max, rows_dev, V,
-                                                                       top_k, mask_value, subtract_max, temperature, vec_ok,
-                                                                       kept_val, kept_idx, kept_cnt, masked_logp);
+    err = rd::launch_chained(vocab_topk_kernel<__nv_bfloat16>, dim3(rows_max), dim3(kTopkThreads), 0, s, 1,
+                             (const __nv_bfloat16*)logits, ld, rows_max, rows_dev, V, top_k, mask_value, subtract_max, temperature,
+                             vec_ok, kept_val, kept_idx, kept_cnt, masked_logp);
   } else {
     return RD_ERR_DTYPE;
   }
-  RD_CHECK_LAUNCH();
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 
@@ -544,10 +557,13 @@ extern "C" int rd_beam_select(int B, int W, int Lb, int k, int V, const float* k
              RD_ERR_SIZE);
   RD_REQUIRE((int64_t)W * V < (int64_t)INT32_MAX, RD_ERR_SIZE);
   const size_t smem = (size_t)W * W * sizeof(float) + (size_t)W * sizeof(int);
-  beam_select_kernel<<<dim3(B, kSelSplit), kSelThreads, smem, (cudaStream_t)stream>>>(W, Lb, k, V, kept_val, kept_idx, kept_cnt, score_in,
-                                                                    score_out, beams_in, beams_out, anc_in, anc_out,
-                                                                    parent_out);
-  RD_CHECK_LAUNCH();
+  cudaError_t err = rd::launch_chained(beam_select_kernel, dim3(B, kSelSplit), dim3(kSelThreads), smem, (cudaStream_t)stream, 1, W, Lb, k, V,
+                                       kept_val, kept_idx, kept_cnt, score_in, score_out, beams_in, beams_out, anc_in, anc_out,
+                                       parent_out);
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 

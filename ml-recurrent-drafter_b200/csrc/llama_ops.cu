@@ -8,6 +8,8 @@ namespace {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int64_t* __restrict__ ids, T* __restrict__ out,
                                     int m_max, const int32_t* __restrict__ m_dev, int H, int vec) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   const int t = blockIdx.x;
   if (t >= rd::live_rows(m_dev, m_max)) return;
   const T* src = table + ids[t] * (int64_t)H;
@@ -153,6 +155,8 @@ __global__ void __launch_bounds__(kRopeThreads) rope_kv_write_kernel(
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, int64_t ld, int m_max,
                                                           const int32_t* __restrict__ m_dev, int V,
                                                           int32_t* __restrict__ out32, int64_t* __restrict__ out64) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   const int t = blockIdx.x;
   if (t >= rd::live_rows(m_dev, m_max)) return;
   const float* row = logits + (int64_t)t * ld;
@@ -196,6 +200,8 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restric
 __global__ void emit_tokens_kernel(const int64_t* __restrict__ token_buf, int max_len, const int32_t* __restrict__ kv_begin,
                                    const int32_t* __restrict__ kv_len, const int64_t* __restrict__ next_tokens,
                                    int64_t pad_id, int out_len, int64_t* __restrict__ out) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   const int b = blockIdx.x;
   const int len = kv_len[b], begin = kv_begin[b];
   const int lead = out_len - 1 - len;  // pad ids on the left
@@ -273,8 +279,13 @@ extern "C" int rd_embed_gather(int dtype, const void* table, const int64_t* ids,
   cudaStream_t s = (cudaStream_t)stream;
   const int esz = dtype == RD_F32 ? 4 : 2;
   const int vec = ((H * esz) % 16 == 0) && ((((uintptr_t)table | (uintptr_t)out) & 15) == 0);
-  RD_DISPATCH_T(dtype, (embed_gather_kernel<T><<<m_max, 256, 0, s>>>((const T*)table, ids, (T*)out, m_max, m_dev, H, vec)));
-  RD_CHECK_LAUNCH();
+  cudaError_t err = cudaSuccess;
+  RD_DISPATCH_T(dtype, (err = rd::launch_chained(embed_gather_kernel<T>, dim3(m_max), dim3(256), 0, s, 1, (const T*)table, ids, (T*)out,
+                                                 m_max, m_dev, H, vec)));
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 
@@ -323,8 +334,12 @@ extern "C" int rd_argmax_rows(const float* logits, int64_t ld, int m_max, const 
                               int64_t* out64, void* stream) {
   RD_REQUIRE(logits && (out32 || out64), RD_ERR_ARG);
   RD_REQUIRE(m_max >= 1 && V >= 1 && ld >= V, RD_ERR_SIZE);
-  argmax_rows_kernel<<<m_max, 256, 0, (cudaStream_t)stream>>>(logits, ld, m_max, m_dev, V, out32, out64);
-  RD_CHECK_LAUNCH();
+  cudaError_t err = rd::launch_chained(argmax_rows_kernel, dim3(m_max), dim3(256), 0, (cudaStream_t)stream, 1, logits, ld, m_max, m_dev, V,
+                                       out32, out64);
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 
@@ -333,9 +348,12 @@ extern "C" int rd_emit_tokens(const int64_t* token_buf, int max_len, const int32
                               void* stream) {
   RD_REQUIRE(token_buf && kv_begin && kv_len && next_tokens && out, RD_ERR_ARG);
   RD_REQUIRE(B >= 1 && out_len >= 1 && max_len >= 1, RD_ERR_SIZE);
-  emit_tokens_kernel<<<B, 256, 0, (cudaStream_t)stream>>>(token_buf, max_len, kv_begin, kv_len, next_tokens, pad_id,
-                                                         out_len, out);
-  RD_CHECK_LAUNCH();
+  cudaError_t err = rd::launch_chained(emit_tokens_kernel, dim3(B), dim3(256), 0, (cudaStream_t)stream, 1, token_buf, max_len, kv_begin,
+                                       kv_len, next_tokens, pad_id, out_len, out);
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 

@@ -145,6 +145,8 @@ constexpr int kRowsPerCta = 4;  // one warp per batch row
 
 // Phase A: prefix ids, unpacker and n_selected of every row (rows are independent).
 __global__ void __launch_bounds__(kRowsPerCta * 32) tree_pack_ids_kernel(PackArgs a) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   __shared__ int32_t seg[kRowsPerCta][64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * kRowsPerCta + warp;
@@ -154,6 +156,8 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) tree_pack_ids_kernel(PackArg
 // Phase B: each warp sums the counts of the rows before its own (the batch is small), publishes
 // row_start and writes its row's slice of the flat arrays and the bitmask.
 __global__ void __launch_bounds__(kRowsPerCta * 32) tree_pack_emit_kernel(PackArgs a) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x * kRowsPerCta + warp;
   if (b >= a.B) return;
@@ -231,9 +235,13 @@ extern "C" int rd_tree_pack(const int64_t* beams, int B, int W, int Lb, const in
   PackArgs a{beams,      B,          W,       Lb,      kv_begin, kv_len,    prefix_tree, unpacker,  n_selected,
              row_start,  flat_tokens, flat_index, tok_row, tok_pos,  tok_slot,  tree_mask,   mask_words, base_len};
   const int grid = (B + kRowsPerCta - 1) / kRowsPerCta;
-  tree_pack_ids_kernel<<<grid, kRowsPerCta * 32, 0, (cudaStream_t)stream>>>(a);
-  tree_pack_emit_kernel<<<grid, kRowsPerCta * 32, 0, (cudaStream_t)stream>>>(a);
-  RD_CHECK_LAUNCH();
+  cudaError_t err = rd::launch_chained(tree_pack_ids_kernel, dim3(grid), dim3(kRowsPerCta * 32), 0, (cudaStream_t)stream, 1, a);
+  if (err == cudaSuccess)
+    err = rd::launch_chained(tree_pack_emit_kernel, dim3(grid), dim3(kRowsPerCta * 32), 0, (cudaStream_t)stream, 1, a);
+  if (err != cudaSuccess) {
+    rd_set_last_cuda_error((int)err);
+    return RD_ERR_LAUNCH;
+  }
   return RD_OK;
 }
 
