@@ -71,7 +71,7 @@ class ClockSampler:
             self._proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index),
                  "--query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap", "--format=csv,noheader,nounits", "-lms", "200"],
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw", "--format=csv,noheader,nounits", "-lms", "200"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -92,8 +92,15 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        watts = []
+        for r in self.rows:
+            try:
+                watts.append(float(r[6]))
+            except (IndexError, ValueError):
+                pass
+        watts.sort()
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+                "samples": len(mhz), "power_w": round(watts[len(watts) // 2], 1) if watts else None}
 
 
 # ------------------------------------------------------------------------------------------------
