@@ -248,10 +248,7 @@ int launch(int dtype, const CommitArgs& a, cudaStream_t s) {
   } else {
     return RD_ERR_DTYPE;
   }
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 

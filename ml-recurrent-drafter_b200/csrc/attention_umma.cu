@@ -597,10 +597,7 @@ static int attention_tc_launch(const void* plan, void* out, const int32_t* row_s
   cudaError_t err = rd::launch_chained(kern, grid, dim3(kThreads), kSmemBytes, (cudaStream_t)stream, 1, p->map_q, p->map_k, p->map_v,
                                        (__nv_bfloat16*)out, row_start, kv_begin, base_len, p->nh, p->nkv, p->max_len, mode,
                                        tree_mask, mask_words, scale_log2, status, n_split, (float*)workspace);
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   if (n_split > 1) {
     attention_merge_kernel<<<dim3(p->m_max, p->nh), HD, 0, (cudaStream_t)stream>>>((const float*)workspace, (__nv_bfloat16*)out,
                                                                                  row_start, p->B, p->nh, n_split);

@@ -511,10 +511,7 @@ extern "C" int rd_drafter_prepare(int dtype, const void* embed, const int64_t* b
                              beams, parent, (const __nv_bfloat16*)ctx, (__nv_bfloat16*)a, (__nv_bfloat16*)x, W, Lb, H, k, vec);
   else
     return RD_ERR_DTYPE;
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 
@@ -539,10 +536,7 @@ extern "C" int rd_vocab_topk(int logits_dtype, const void* logits, int64_t ld, i
   } else {
     return RD_ERR_DTYPE;
   }
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 
@@ -560,10 +554,7 @@ extern "C" int rd_beam_select(int B, int W, int Lb, int k, int V, const float* k
   cudaError_t err = rd::launch_chained(beam_select_kernel, dim3(B, kSelSplit), dim3(kSelThreads), smem, (cudaStream_t)stream, 1, W, Lb, k, V,
                                        kept_val, kept_idx, kept_cnt, score_in, score_out, beams_in, beams_out, anc_in, anc_out,
                                        parent_out);
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 

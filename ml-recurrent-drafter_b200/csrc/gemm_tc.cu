@@ -928,10 +928,7 @@ int launch_cluster2(Kern kern, int grid, int smem_bytes, cudaStream_t s, const G
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   cudaError_t err = rd::launch_chained(kern, dim3(grid), dim3(kThreads), smem_bytes, s, 2, p->map_a, p->map_w, e, p->m_max, m_dev,
                                        p->N, p->K, status);
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 
@@ -1063,9 +1060,6 @@ extern "C" int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, 
 extern "C" int rd_gemm_set_timing(void* acc) {
   unsigned long long* p = static_cast<unsigned long long*>(acc);
   cudaError_t err = cudaMemcpyToSymbol(g_gemm_timing, &p, sizeof(p));
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }

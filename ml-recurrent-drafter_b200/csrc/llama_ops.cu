@@ -282,10 +282,7 @@ extern "C" int rd_embed_gather(int dtype, const void* table, const int64_t* ids,
   cudaError_t err = cudaSuccess;
   RD_DISPATCH_T(dtype, (err = rd::launch_chained(embed_gather_kernel<T>, dim3(m_max), dim3(256), 0, s, 1, (const T*)table, ids, (T*)out,
                                                  m_max, m_dev, H, vec)));
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 
@@ -299,10 +296,7 @@ extern "C" int rd_rmsnorm(int dtype, const void* x, const void* weight, void* y,
   cudaError_t err = cudaSuccess;
   RD_DISPATCH_T(dtype, (err = rd::launch_chained(rmsnorm_kernel<T>, dim3(m_max), dim3(256), 0, s, 1, (const T*)x, (const T*)weight,
                                                  (T*)y, m_max, m_dev, H, eps, vectorised)));
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 
@@ -323,10 +317,7 @@ extern "C" int rd_rope_kv_write(int dtype, const void* qkv, void* q_out, void* k
   RD_DISPATCH_T(dtype, (err = rd::launch_chained(rope_kv_write_kernel<T>, dim3(m_max), dim3(kRopeThreads), 0, s, 1, (const T*)qkv, (T*)q_out,
                                                  (T*)k_cache, (T*)v_cache, tok_row, tok_pos, tok_slot, cos_table, sin_table,
                                                  n_pos, m_max, m_dev, nh, nkv, hd, max_len)));
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 
@@ -336,10 +327,7 @@ extern "C" int rd_argmax_rows(const float* logits, int64_t ld, int m_max, const 
   RD_REQUIRE(m_max >= 1 && V >= 1 && ld >= V, RD_ERR_SIZE);
   cudaError_t err = rd::launch_chained(argmax_rows_kernel, dim3(m_max), dim3(256), 0, (cudaStream_t)stream, 1, logits, ld, m_max, m_dev, V,
                                        out32, out64);
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 
@@ -350,10 +338,7 @@ extern "C" int rd_emit_tokens(const int64_t* token_buf, int max_len, const int32
   RD_REQUIRE(B >= 1 && out_len >= 1 && max_len >= 1, RD_ERR_SIZE);
   cudaError_t err = rd::launch_chained(emit_tokens_kernel, dim3(B), dim3(256), 0, (cudaStream_t)stream, 1, token_buf, max_len, kv_begin,
                                        kv_len, next_tokens, pad_id, out_len, out);
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 

@@ -25,6 +25,15 @@
     }                                                       \
   } while (0)
 
+// The same for a cudaError_t already in hand (rd::launch_chained() returns one).
+#define RD_CHECK_CHAINED(err)                               \
+  do {                                                      \
+    if ((err) != cudaSuccess) {                             \
+      rd_set_last_cuda_error((int)(err));                   \
+      return RD_ERR_LAUNCH;                                 \
+    }                                                       \
+  } while (0)
+
 void rd_set_last_cuda_error(int e);
 // 1 unless the environment variable RD_PDL is "0" (read once): launch the kernels of the decode
 // chain with programmatic stream serialisation so that a kernel's launch and prologue overlap the

@@ -238,10 +238,7 @@ extern "C" int rd_tree_pack(const int64_t* beams, int B, int W, int Lb, const in
   cudaError_t err = rd::launch_chained(tree_pack_ids_kernel, dim3(grid), dim3(kRowsPerCta * 32), 0, (cudaStream_t)stream, 1, a);
   if (err == cudaSuccess)
     err = rd::launch_chained(tree_pack_emit_kernel, dim3(grid), dim3(kRowsPerCta * 32), 0, (cudaStream_t)stream, 1, a);
-  if (err != cudaSuccess) {
-    rd_set_last_cuda_error((int)err);
-    return RD_ERR_LAUNCH;
-  }
+  RD_CHECK_CHAINED(err);
   return RD_OK;
 }
 
