@@ -406,6 +406,14 @@ def run_cpu(args, as_reference_arm: bool):
 
     lc, R, B, W, Lb, Lp, gen, dt, greedy, temp = CONFIGS[args.config]
     cores = os.cpu_count() or 1
+    try:
+        # a launcher may have exported OMP_NUM_THREADS=1 (torchrun does): give the BLAS every host core back
+        from threadpoolctl import threadpool_info, threadpool_limits
+
+        threadpool_limits(limits=cores)
+        cores = max([int(i.get("num_threads", 1)) for i in threadpool_info()] or [1])
+    except ImportError:
+        cores = int(os.environ.get("OMP_NUM_THREADS", cores))
     rows = 1 if args.config != "c1" else B
     steps = (max(args.warmup, 1) + args.steps) if as_reference_arm else 3
     budget = 240.0 if as_reference_arm else 40.0
