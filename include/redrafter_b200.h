@@ -106,9 +106,12 @@ RD_API int rd_tree_pack_reference_layout(int B, int W, int Lb, const int32_t* un
  * rd_drafter_prepare builds the input of the recurrent update for iteration k
  * (modeling_drafter.py:193-197): a[r, 0:H] = embed[beams[b,w,k]], a[r, H:2H] = state of the
  * parent beam (x[b*W+parent[b,w], H:2H]; zeros when k == 0), and, when k == 0, x[r, 0:H] = ctx[b]
- * (the constant context half of the LM-head input, :174).  r = b*W + w; a, x are [B*W, 2H]. */
+ * (the constant context half of the LM-head input, :174).  r = b*W + w; a, x are [B*W, 2H].
+ * additive != 0 serves drafters built with rnn = false, whose state update has no projections
+ * (state = embedding + state, modeling_drafter.py:196): a[r, H:2H] then holds the new state itself
+ * (embedding + parent state, rounded once to the model type) and the caller copies it into x[r, H:2H]. */
 RD_API int rd_drafter_prepare(int dtype, const void* embed, const int64_t* beams, const int32_t* parent, const void* ctx,
-                       void* a, void* x, int B, int W, int Lb, int H, int k, void* stream);
+                       void* a, void* x, int B, int W, int Lb, int H, int k, int additive, void* stream);
 
 /* Per-row top-k warp + log-softmax of a (rows, V) logits matrix, sparse output.  Replaces
  * maintain_logits, warp_logits and log_softmax (modeling_drafter.py:63-99, 201-203) and, for the
@@ -132,6 +135,14 @@ RD_API int rd_vocab_topk(int logits_dtype, const void* logits, int64_t ld, int r
  * gathered from the parent, column k+1 is the new token.  anc_in/out [B,W,Lb-1]: row index
  * (within the batch row) that produced the log-probs of position j of every surviving beam.
  * Requires W <= RD_TOPK_MAX_KEPT candidates per row to be exact (see kept_cnt). */
+/* rd_vocab_topk for logits produced by rd_gemm_bf16_tc_slicemax: the threshold comes from the slice
+ * maxima and only the slices that can hold kept entries are read (about a tenth of the row), with the
+ * same results as rd_vocab_topk, bit for bit.  V a multiple of 32, rows 16-byte aligned. */
+RD_API int rd_vocab_topk_sliced(int logits_dtype, const void* logits, int64_t ld, int rows_max, const int32_t* rows_dev, int V,
+                         int top_k, float mask_value, int subtract_max, float temperature, const float* slice_max,
+                         int64_t slice_ld, float* kept_val, int32_t* kept_idx, int32_t* kept_cnt, float* masked_logp,
+                         void* stream);
+
 RD_API int rd_beam_select(int B, int W, int Lb, int k, int V, const float* kept_val, const int32_t* kept_idx,
                    const int32_t* kept_cnt, const float* score_in, float* score_out, const int64_t* beams_in,
                    int64_t* beams_out, const int32_t* anc_in, int32_t* anc_out, int32_t* parent_out, void* stream);
@@ -175,12 +186,25 @@ RD_API int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, void
                              const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv, int hd,
                              int max_len, int32_t* status, void* stream);
 
-/* Measurement aid: with acc != NULL (two 64-bit device counters, zeroed by the caller) every
- * rd_gemm_bf16_tc* launch adds to acc[0] the nanoseconds its first CTA spent between the end of its
- * dependency wait and its last tile (%globaltimer) and to acc[1] the launch's 2*M*N*K, M read on
- * the device.  acc = NULL switches it off (the default).  A cudaMemcpyToSymbol: call it while no
- * GEMM of this library is running. */
-RD_API int rd_gemm_set_timing(void* acc);
+/* The LM head of the greedy verify step with the arg-max over the vocabulary done in its epilogue
+ * (modeling_llama.py:272 followed by recurrent_drafting.py:52): `plan` holds (final hidden states,
+ * lm_head weight [V, H]); the fp32 logits are never written.  Every 32 consecutive vocabulary ids of a
+ * token are reduced to (largest logit, first id holding it) in the GEMM epilogue and a second, small
+ * kernel merges the V/32 partial results per token; equal logits resolve to the smaller id, as the
+ * separate rd_argmax_rows does, and the logits compared are the same fp32 accumulators it would read.
+ * `workspace` (device, 16-byte aligned) holds the partial results; its size comes from
+ * rd_gemm_argmax_workspace_bytes(m_max of the plan, V); RD_ERR_CAPACITY if it is too small. */
+RD_API int64_t rd_gemm_argmax_workspace_bytes(int m_max, int N);
+RD_API int rd_gemm_bf16_tc_argmax(const void* plan, const int32_t* m_dev, void* workspace, int64_t workspace_bytes,
+                           int32_t* out32, int64_t* out64, int32_t* status, void* stream);
+
+/* rd_gemm_bf16_tc with RD_EPI_NONE that also writes, for every token and every slice of 32 consecutive
+ * output features, the largest value of the slice as stored in C: slice_max[s * slice_ld + token],
+ * slice_ld >= m_max.  Feeds rd_vocab_topk_sliced (the drafter's vocabulary head, modeling_drafter.py:
+ * 127-131, and the LM head of the sampling verify step).  N must be a multiple of 32, C rows 16-byte
+ * aligned. */
+RD_API int rd_gemm_bf16_tc_slicemax(const void* plan, int out_dtype, void* C, int64_t ldc, const int32_t* m_dev,
+                             float* slice_max, int64_t slice_ld, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Llama verify forward pieces (recurrent_drafting/modeling_llama.py). */

@@ -10,7 +10,7 @@ namespace {
 template <typename T>
 __global__ void drafter_prepare_kernel(const T* __restrict__ embed, const int64_t* __restrict__ beams,
                                        const int32_t* __restrict__ parent, const T* __restrict__ ctx, T* __restrict__ a,
-                                       T* __restrict__ x, int W, int Lb, int H, int k, int vec) {
+                                       T* __restrict__ x, int W, int Lb, int H, int k, int vec, int additive) {
   rd::pdl_launch_dependents();
   rd::pdl_wait();
   const int r = blockIdx.x;
@@ -26,15 +26,25 @@ __global__ void drafter_prepare_kernel(const T* __restrict__ embed, const int64_
     // 16-byte copies: a = [embedding(token), parent state or zeros]; x[:H] = context (first iteration only)
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     for (int d = threadIdx.x; d < H / VEC; d += blockDim.x) {
-      reinterpret_cast<uint4*>(arow)[d] = reinterpret_cast<const uint4*>(e)[d];
-      reinterpret_cast<uint4*>(arow + H)[d] = s ? reinterpret_cast<const uint4*>(s)[d] : zero;
+      const uint4 ev = reinterpret_cast<const uint4*>(e)[d];
+      uint4 sv = s ? reinterpret_cast<const uint4*>(s)[d] : zero;
+      if (additive) {
+        // drafter without the recurrent projections: new state = embedding + parent state
+        const T* ep = reinterpret_cast<const T*>(&ev);
+        T* sp = reinterpret_cast<T*>(&sv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) sp[i] = rd::Num<T>::from_f(rd::Num<T>::to_f(ep[i]) + rd::Num<T>::to_f(sp[i]));
+      }
+      reinterpret_cast<uint4*>(arow)[d] = ev;
+      reinterpret_cast<uint4*>(arow + H)[d] = sv;
       if (k == 0) reinterpret_cast<uint4*>(xrow)[d] = reinterpret_cast<const uint4*>(c)[d];
     }
     return;
   }
   for (int d = threadIdx.x; d < H; d += blockDim.x) {
     arow[d] = e[d];
-    arow[H + d] = s ? s[d] : rd::Num<T>::from_f(0.f);
+    const float sv = s ? rd::Num<T>::to_f(s[d]) : 0.f;
+    arow[H + d] = rd::Num<T>::from_f(additive ? rd::Num<T>::to_f(e[d]) + sv : sv);
     if (k == 0) xrow[d] = c[d];
   }
 }
@@ -61,7 +71,32 @@ struct RowReader {
   const T* src;
   int V;
   bool vec;  // 16-byte loads allowed
+  // Optional per-slice maxima of this row (slice = 32 consecutive ids), element s at smax[s * smax_ld], written
+  // by the GEMM that produced the row: with them the row is read only where it can hold values >= a bound.
+  const float* smax;
+  int64_t smax_ld;
   static constexpr int VEC = 16 / sizeof(T);
+  // calls f(slice maximum) for this thread's share of the slices
+  template <typename F>
+  __device__ __forceinline__ void for_each_slice_max(int tid, F f) const {
+    const int n_slices = V >> 5;
+    for (int sl = tid; sl < n_slices; sl += kTopkThreads) f(smax[(int64_t)sl * smax_ld]);
+  }
+  // calls f(value, index) for the elements of the slices whose maximum is >= bound
+  template <typename F>
+  __device__ __forceinline__ void for_each_in_slices_at_least(int tid, float bound, F f) const {
+    const int n_slices = V >> 5;
+    for (int sl = tid; sl < n_slices; sl += kTopkThreads) {
+      if (!(smax[(int64_t)sl * smax_ld] >= bound)) continue;
+#pragma unroll
+      for (int c = 0; c < 32 / VEC; ++c) {
+        T e[VEC];
+        *reinterpret_cast<uint4*>(e) = reinterpret_cast<const uint4*>(src + sl * 32)[c];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) f(rd::Num<T>::to_f(e[j]), sl * 32 + c * VEC + j);
+      }
+    }
+  }
   // calls f(value, index) for this thread's share of the row
   template <typename F>
   __device__ __forceinline__ void for_each(int tid, F f) const {
@@ -192,20 +227,27 @@ __device__ void topk_radix_path(const RowReader<T>& row, TopkShared& sh, int top
 template <typename T>
 __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
     const T* __restrict__ logits, int64_t ld, int rows_max, const int32_t* __restrict__ rows_dev, int V, int top_k,
-    float mask_value, int subtract_max, float temperature, int vec_ok, float* __restrict__ kept_val,
-    int32_t* __restrict__ kept_idx, int32_t* __restrict__ kept_cnt, float* __restrict__ masked_logp) {
+    float mask_value, int subtract_max, float temperature, int vec_ok, const float* __restrict__ slice_max, int64_t slice_ld,
+    float* __restrict__ kept_val, int32_t* __restrict__ kept_idx, int32_t* __restrict__ kept_cnt,
+    float* __restrict__ masked_logp) {
   rd::pdl_launch_dependents();
   rd::pdl_wait();
   const int row_id = blockIdx.x;
   if (row_id >= rd::live_rows(rows_dev, rows_max)) return;
   __shared__ TopkShared sh;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  RowReader<T> row{logits + (int64_t)row_id * ld, V, vec_ok != 0};
+  const bool sliced = slice_max != nullptr;
+  RowReader<T> row{logits + (int64_t)row_id * ld, V, vec_ok != 0, sliced ? slice_max + row_id : nullptr, slice_ld};
   const int K = top_k < V ? top_k : V;
 
-  // 1. thread maxima -> lower bound T0 of the K-th largest value, and the row maximum
+  // 1. thread maxima -> lower bound T0 of the K-th largest value, and the row maximum.  With slice maxima
+  //    the thread maxima come from them (each is an element of the row, distinct slices hold distinct
+  //    elements), so this pass reads V/32 floats instead of the row.
   float lm = -INFINITY;
-  row.for_each(tid, [&](float f, int) { lm = fmaxf(lm, f); });
+  if (sliced)
+    row.for_each_slice_max(tid, [&](float f) { lm = fmaxf(lm, f); });
+  else
+    row.for_each(tid, [&](float f, int) { lm = fmaxf(lm, f); });
   if (tid == 0) {
     sh.ccount = 0;
     sh.gt = 0;
@@ -246,8 +288,8 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
   __syncthreads();
   const float t0 = sh.t0, mx = sh.mx;
 
-  // 2. candidates
-  row.for_each(tid, [&](float f, int v) {
+  // 2. candidates (every element >= T0 lies in a slice whose maximum is >= T0)
+  auto take = [&](float f, int v) {
     if (f >= t0) {
       const int s = atomicAdd(&sh.ccount, 1);
       if (s < kCandCap) {
@@ -255,7 +297,11 @@ __global__ void __launch_bounds__(kTopkThreads) vocab_topk_kernel(
         sh.cidx[s] = v;
       }
     }
-  });
+  };
+  if (sliced)
+    row.for_each_in_slices_at_least(tid, t0, take);
+  else
+    row.for_each(tid, take);
   __syncthreads();
   const int n_cand = sh.ccount;
   int cnt;
@@ -493,7 +539,8 @@ __global__ void sample_sparse_kernel(const float* __restrict__ kept_val, const i
 }  // namespace
 
 extern "C" int rd_drafter_prepare(int dtype, const void* embed, const int64_t* beams, const int32_t* parent,
-                                  const void* ctx, void* a, void* x, int B, int W, int Lb, int H, int k, void* stream) {
+                                  const void* ctx, void* a, void* x, int B, int W, int Lb, int H, int k, int additive,
+                                  void* stream) {
   RD_REQUIRE(embed && beams && ctx && a && x, RD_ERR_ARG);
   RD_REQUIRE(k == 0 || parent, RD_ERR_ARG);
   RD_REQUIRE(B >= 1 && W >= 1 && W <= RD_MAX_BEAM_WIDTH && Lb >= 2 && Lb <= RD_MAX_BEAM_LENGTH && H >= 1 && k >= 0 &&
@@ -505,12 +552,43 @@ extern "C" int rd_drafter_prepare(int dtype, const void* embed, const int64_t* b
   cudaError_t err = cudaSuccess;
   if (dtype == RD_F32)
     err = rd::launch_chained(drafter_prepare_kernel<float>, dim3(B * W), dim3(256), 0, s, 1, (const float*)embed, beams, parent,
-                             (const float*)ctx, (float*)a, (float*)x, W, Lb, H, k, vec);
+                             (const float*)ctx, (float*)a, (float*)x, W, Lb, H, k, vec, additive);
   else if (dtype == RD_BF16)
     err = rd::launch_chained(drafter_prepare_kernel<__nv_bfloat16>, dim3(B * W), dim3(256), 0, s, 1, (const __nv_bfloat16*)embed,
-                             beams, parent, (const __nv_bfloat16*)ctx, (__nv_bfloat16*)a, (__nv_bfloat16*)x, W, Lb, H, k, vec);
+                             beams, parent, (const __nv_bfloat16*)ctx, (__nv_bfloat16*)a, (__nv_bfloat16*)x, W, Lb, H, k, vec, additive);
   else
     return RD_ERR_DTYPE;
+  RD_CHECK_CHAINED(err);
+  return RD_OK;
+}
+
+static int vocab_topk_launch(int logits_dtype, const void* logits, int64_t ld, int rows_max, const int32_t* rows_dev, int V,
+                             int top_k, float mask_value, int subtract_max, float temperature, const float* slice_max,
+                             int64_t slice_ld, float* kept_val, int32_t* kept_idx, int32_t* kept_cnt, float* masked_logp,
+                             void* stream) {
+  RD_REQUIRE(logits && kept_val && kept_idx && kept_cnt && masked_logp, RD_ERR_ARG);
+  RD_REQUIRE(rows_max >= 1 && V >= 1 && top_k >= 1 && top_k <= RD_TOPK_MAX_KEPT && ld >= V, RD_ERR_SIZE);
+  RD_REQUIRE(temperature > 0.f, RD_ERR_ARG);
+  if (slice_max) {
+    // whole slices of 32 ids, read with 16-byte loads
+    RD_REQUIRE(V % 32 == 0 && slice_ld >= rows_max, RD_ERR_SIZE);
+    RD_REQUIRE((uintptr_t)logits % 16 == 0 && (ld * (logits_dtype == RD_F32 ? 4 : 2)) % 16 == 0, RD_ERR_ALIGN);
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t err = cudaSuccess;
+  if (logits_dtype == RD_F32) {
+    const int vec_ok = ((uintptr_t)logits % 16 == 0) && ((ld * 4) % 16 == 0);
+    err = rd::launch_chained(vocab_topk_kernel<float>, dim3(rows_max), dim3(kTopkThreads), 0, s, 1, (const float*)logits, ld, rows_max,
+                             rows_dev, V, top_k, mask_value, subtract_max, temperature, vec_ok, slice_max, slice_ld, kept_val, kept_idx,
+                             kept_cnt, masked_logp);
+  } else if (logits_dtype == RD_BF16) {
+    const int vec_ok = ((uintptr_t)logits % 16 == 0) && ((ld * 2) % 16 == 0);
+    err = rd::launch_chained(vocab_topk_kernel<__nv_bfloat16>, dim3(rows_max), dim3(kTopkThreads), 0, s, 1,
+                             (const __nv_bfloat16*)logits, ld, rows_max, rows_dev, V, top_k, mask_value, subtract_max, temperature,
+                             vec_ok, slice_max, slice_ld, kept_val, kept_idx, kept_cnt, masked_logp);
+  } else {
+    return RD_ERR_DTYPE;
+  }
   RD_CHECK_CHAINED(err);
   return RD_OK;
 }
@@ -518,26 +596,17 @@ extern "C" int rd_drafter_prepare(int dtype, const void* embed, const int64_t* b
 extern "C" int rd_vocab_topk(int logits_dtype, const void* logits, int64_t ld, int rows_max, const int32_t* rows_dev,
                              int V, int top_k, float mask_value, int subtract_max, float temperature, float* kept_val,
                              int32_t* kept_idx, int32_t* kept_cnt, float* masked_logp, void* stream) {
-  RD_REQUIRE(logits && kept_val && kept_idx && kept_cnt && masked_logp, RD_ERR_ARG);
-  RD_REQUIRE(rows_max >= 1 && V >= 1 && top_k >= 1 && top_k <= RD_TOPK_MAX_KEPT && ld >= V, RD_ERR_SIZE);
-  RD_REQUIRE(temperature > 0.f, RD_ERR_ARG);
-  cudaStream_t s = (cudaStream_t)stream;
-  cudaError_t err = cudaSuccess;
-  if (logits_dtype == RD_F32) {
-    const int vec_ok = ((uintptr_t)logits % 16 == 0) && ((ld * 4) % 16 == 0);
-    err = rd::launch_chained(vocab_topk_kernel<float>, dim3(rows_max), dim3(kTopkThreads), 0, s, 1, (const float*)logits, ld, rows_max,
-                             rows_dev, V, top_k, mask_value, subtract_max, temperature, vec_ok, kept_val, kept_idx, kept_cnt,
-                             masked_logp);
-  } else if (logits_dtype == RD_BF16) {
-    const int vec_ok = ((uintptr_t)logits % 16 == 0) && ((ld * 2) % 16 == 0);
-    err = rd::launch_chained(vocab_topk_kernel<__nv_bfloat16>, dim3(rows_max), dim3(kTopkThreads), 0, s, 1,
-                             (const __nv_bfloat16*)logits, ld, rows_max, rows_dev, V, top_k, mask_value, subtract_max, temperature,
-                             vec_ok, kept_val, kept_idx, kept_cnt, masked_logp);
-  } else {
-    return RD_ERR_DTYPE;
-  }
-  RD_CHECK_CHAINED(err);
-  return RD_OK;
+  return vocab_topk_launch(logits_dtype, logits, ld, rows_max, rows_dev, V, top_k, mask_value, subtract_max, temperature, nullptr, 0,
+                           kept_val, kept_idx, kept_cnt, masked_logp, stream);
+}
+
+extern "C" int rd_vocab_topk_sliced(int logits_dtype, const void* logits, int64_t ld, int rows_max, const int32_t* rows_dev,
+                                    int V, int top_k, float mask_value, int subtract_max, float temperature,
+                                    const float* slice_max, int64_t slice_ld, float* kept_val, int32_t* kept_idx,
+                                    int32_t* kept_cnt, float* masked_logp, void* stream) {
+  RD_REQUIRE(slice_max, RD_ERR_ARG);
+  return vocab_topk_launch(logits_dtype, logits, ld, rows_max, rows_dev, V, top_k, mask_value, subtract_max, temperature, slice_max,
+                           slice_ld, kept_val, kept_idx, kept_cnt, masked_logp, stream);
 }
 
 extern "C" int rd_beam_select(int B, int W, int Lb, int k, int V, const float* kept_val, const int32_t* kept_idx,

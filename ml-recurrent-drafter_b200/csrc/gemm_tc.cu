@@ -1,27 +1,35 @@
 // C = epilogue(A * W^T), bf16 operands, fp32 accumulation on the 5th-generation tensor cores.
 //
 // The decode step has few activation rows (M = packed tree tokens, a few hundred to ~1500, known
-// only on the device) and large weights, so the WEIGHT rows ride the MMA's M dimension (128 per
-// tile) and the tokens its N dimension: N may be any multiple of 16 up to 256, chosen per tile at
-// run time, so the token rows are split into equal chunks with almost no padding (M = 900 costs
-// 912 columns instead of 1024 rows).  The accumulator tile is C^T: TMEM lane = output feature,
-// TMEM column = token, so a warp's store of one token covers 32 consecutive features.
+// only on the device) and large weights, so the WEIGHT rows ride the MMA's M dimension and the
+// tokens its N dimension: N may be any multiple of 16 up to 256, chosen per tile at run time, so the
+// token rows are split into equal chunks with almost no padding (M = 900 costs 912 columns instead
+// of 1024 rows).  The accumulator tile is C^T: TMEM lane = output feature, TMEM column = token.
 //
-// Persistent, warp-specialised kernel, one CTA per SM:
-//   warp 0     TMA producer: cp.async.bulk.tensor loads of a 128 x 64 W tile and one or two
-//              128 x 64 token tiles per pipeline stage (128-byte swizzle, no multicast),
-//              completion on an mbarrier;
-//   warp 1     MMA issuer: one elected thread issues tcgen05.mma (M=128, N=tokens, K=16, kind::f16)
-//              from shared-memory descriptors into one of two TMEM accumulator buffers and frees
-//              stages with tcgen05.commit;
-//   warps 2-5  epilogue: tcgen05.ld of the accumulator (each warp its own 32 TMEM lanes), fused
-//              bias / SiLU / residual / SwiGLU, coalesced global stores, overlapped with the next
-//              tile's main loop through the second accumulator buffer.
+// gemm_tc_pair_kernel is the kernel of the hot path (every projection with at least 256 output
+// features): a persistent kernel, one CTA per SM, CTAs paired in clusters of two that share one
+// tcgen05.mma.cta_group::2 of 256 weight rows x (up to 256) tokens x 16:
+//   warp 0     TMA producer in BOTH CTAs: cp.async.bulk.tensor loads (128-byte swizzle, never
+//              multicast) of this CTA's 128 weight rows and of its HALF of the token tile, six
+//              stages of 32 KB; both CTAs' loads complete on the leader's mbarrier;
+//   warp 1     MMA issuer, leader CTA only: one elected thread issues the MMAs for the pair into
+//              one of two TMEM accumulator buffers (each CTA's TMEM receives its 128 rows) and
+//              frees a stage / publishes an accumulator with ONE tcgen05.commit whose arrival is
+//              delivered to the barrier of both CTAs;
+//   warps 2-5  epilogue in both CTAs: tcgen05.ld of the accumulator (each warp its own 32 TMEM
+//              lanes), the fused element-wise part (bias / SiLU / SwiGLU / residual / rotary
+//              embedding + cache append / arg-max or slice maxima over the vocabulary), a transpose
+//              through shared memory to one token per lane and 16-byte global stores, overlapped
+//              with the next tile's main loop through the second accumulator buffer; the peer's
+//              epilogue frees the accumulator with remote mbarrier arrives.
+// gemm_tc_kernel is the single-CTA form of the same design (cta_group::1, 128 weight rows per tile,
+// four stages) for matrices with fewer than 256 output features.
 // Tiles are walked weight-tile-major so that the CTAs running at the same time share W tiles
-// through L2.
+// through L2; GEMMs with few weight tiles cut the tokens finer so that every CTA pair has a tile.
 //
 // Every mbarrier wait is bounded: when a wait gives up the kernel records a code in *status,
-// stops issuing work, lets outstanding bulk copies land, frees its TMEM and returns.
+// stops issuing work, lets outstanding bulk copies land, meets its peer at the final cluster
+// barrier, frees its TMEM and returns.
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -42,11 +50,24 @@ static int g_use_pairs = [] {
   return (v && v[0] == '0') ? 0 : 1;
 }();
 
-// Optional in-kernel timing (rd_gemm_set_timing): acc[0] += nanoseconds CTA 0 spent between its
-// dependency wait and its last tile, acc[1] += 2*M*N*K of the launch.  CTA (pair) 0 owns the largest
-// share of the tiles, so its lifetime is the kernel's duration without launch latency and without
-// the perturbation of event records between dependent launches.
+// Experiment builds only (-DRD_GEMM_TIMING; the shipped library carries none of this): acc[0] +=
+// nanoseconds CTA 0 spent between its dependency wait and its last tile, acc[1] += 2*M*N*K of the
+// launch.  CTA (pair) 0 owns the largest share of the tiles, so its lifetime is the kernel's duration
+// without launch latency and without the perturbation of event records between dependent launches.
+#ifdef RD_GEMM_TIMING
 __device__ unsigned long long* g_gemm_timing = nullptr;
+#define RD_TIMING_BEGIN()                                                                                      \
+  unsigned long long* const timing = (blockIdx.x == 0 && threadIdx.x == 0) ? g_gemm_timing : nullptr;           \
+  const uint64_t t_begin = timing ? global_ns() : 0
+#define RD_TIMING_END(M, N, K)                                                                                 \
+  if (timing) {                                                                                                \
+    atomicAdd(timing, (unsigned long long)(global_ns() - t_begin));                                            \
+    atomicAdd(timing + 1, 2ull * (unsigned long long)(M) * (unsigned long long)(N) * (unsigned long long)(K)); \
+  }
+#else
+#define RD_TIMING_BEGIN() do { } while (0)
+#define RD_TIMING_END(M, N, K) do { } while (0)
+#endif
 
 struct GemmPlan {
   CUtensorMap map_a;  // activations [m_max, K], box 64 x 128
@@ -206,9 +227,19 @@ struct EpiArgs {
   const float* cos_t;
   const float* sin_t;
   int n_pos, nh, nkv, max_len;
+  // kEpiArgmax / kEpiSliceMax only: per (32-feature slice, token) partial results, laid out [slice][part_ld]
+  float* part_val;
+  int32_t* part_idx;
+  int64_t part_ld;
 };
 
 constexpr int kEpiQkvRope = 6;  // internal epilogue code (not one of RD_EPI_*): reached through rd_gemm_bf16_tc_qkv_rope
+// LM head of the greedy verify step: no output matrix; every epilogue warp reduces its 32 output features
+// (vocabulary ids) of each token to (largest logit, first id holding it) and a small kernel merges the slices
+constexpr int kEpiArgmax = 7;
+// plain output plus the largest stored value of every (32-feature slice, token): lets the vocabulary top-k
+// that follows find its threshold from the slice maxima and read only the slices that can hold kept entries
+constexpr int kEpiSliceMax = 8;
 
 constexpr int kScrLd = 36;  // floats per scratch row: 16-byte aligned rows, conflict-free float4 reads
 
@@ -327,10 +358,15 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
   const int tok = tok0 + lane;
   if (tok < tok_limit) {
     if (kRes) res.add_to(o);
+    float smax = -INFINITY;  // kEpiSliceMax: largest value of this token's 32 features AS STORED
     if (OUT_F32) {
       float4* dst = reinterpret_cast<float4*>((float*)e.C + (int64_t)tok * e.ldc + out0);
 #pragma unroll
       for (int j = 0; j < kOut / 4; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+      if (EPI == kEpiSliceMax) {
+#pragma unroll
+        for (int j = 0; j < kOut; ++j) smax = fmaxf(smax, o[j]);
+      }
     } else {
       uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)e.C + (int64_t)tok * e.ldc + out0);
 #pragma unroll
@@ -338,12 +374,47 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
         uint4 pk;
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(o[8 * j + 2 * t], o[8 * j + 2 * t + 1]);
+        for (int t = 0; t < 4; ++t) {
+          h[t] = __floats2bfloat162_rn(o[8 * j + 2 * t], o[8 * j + 2 * t + 1]);
+          if (EPI == kEpiSliceMax) {
+            const float2 r = __bfloat1622float2(h[t]);
+            smax = fmaxf(smax, fmaxf(r.x, r.y));
+          }
+        }
         dst[j] = pk;
       }
     }
+    if (EPI == kEpiSliceMax) e.part_val[(int64_t)(n_warp0 >> 5) * e.part_ld + tok] = smax;
   }
   (void)n_out_total;
+}
+
+// kEpiArgmax: one 32-token block of a tile.  v: accumulator values (lane = vocabulary id n_warp0 + lane,
+// i = token).  After the transpose each lane owns one token and scans its 32 ids in ascending order, so
+// the first id among equal logits wins, as torch.argmax / the separate row kernel decide.
+__device__ __forceinline__ void epilogue_argmax_block(const float* v, const EpiArgs& e, float* scr, int lane, int n_warp0,
+                                                      int tok0, int tok_limit, int N) {
+  const bool in_range = n_warp0 + lane < N;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = in_range ? v[i] : -INFINITY;
+  __syncwarp();
+  float best = -INFINITY;
+  int bj = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float4 f = *reinterpret_cast<const float4*>(scr + lane * kScrLd + 4 * j);
+    if (f.x > best) { best = f.x; bj = 4 * j; }
+    if (f.y > best) { best = f.y; bj = 4 * j + 1; }
+    if (f.z > best) { best = f.z; bj = 4 * j + 2; }
+    if (f.w > best) { best = f.w; bj = 4 * j + 3; }
+  }
+  __syncwarp();  // the scratch is reused by the next block
+  const int tok = tok0 + lane;
+  if (tok < tok_limit) {
+    const int64_t at = (int64_t)(n_warp0 >> 5) * e.part_ld + tok;
+    e.part_val[at] = best;
+    e.part_idx[at] = n_warp0 + bj;
+  }
 }
 
 // Epilogue block of the QKV projection with fused rotary embedding (head_dim 128 = one CTA's 128
@@ -470,8 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // count, the activations, the output) is valid once the kernels before this one have finished
   rd::pdl_wait();
   const int M = rd::live_rows(m_dev, m_max);
-  unsigned long long* const timing = (blockIdx.x == 0 && threadIdx.x == 0) ? g_gemm_timing : nullptr;
-  const uint64_t t_begin = timing ? global_ns() : 0;
+  RD_TIMING_BEGIN();
   const int w_tiles = (N + BM - 1) / BM;
   const Chunking ch = make_chunking(M, w_tiles, gridDim.x);
   const int total_tiles = M > 0 ? w_tiles * ch.n_chunks : 0;
@@ -595,6 +665,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         if (EPI == kEpiQkvRope) {
           epilogue_rope_block(v, epi, scratch, quarter, lane, (n_warp0 - quarter * 32) / 128, tok_base + c, tok_limit);
+        } else if (EPI == kEpiArgmax) {
+          epilogue_argmax_block(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N);
         } else {
           epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok);
           epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
@@ -609,10 +681,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   tc_fence_before();
   __syncthreads();
-  if (timing) {
-    atomicAdd(timing, (unsigned long long)(global_ns() - t_begin));
-    atomicAdd(timing + 1, 2ull * (unsigned long long)M * (unsigned long long)N * (unsigned long long)K);
-  }
+  RD_TIMING_END(M, N, K);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kMaxChunk) : "memory");
@@ -740,8 +809,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = *tmem_slot;
   rd::pdl_wait();  // global memory is valid once the kernels before this one have finished
   const int M = rd::live_rows(m_dev, m_max);
-  unsigned long long* const timing = (blockIdx.x == 0 && threadIdx.x == 0) ? g_gemm_timing : nullptr;
-  const uint64_t t_begin = timing ? global_ns() : 0;
+  RD_TIMING_BEGIN();
   const int w_pairs = (N + 2 * BM - 1) / (2 * BM);
   const Chunking ch = make_chunking(M, w_pairs, n_pairs);
   const int total_tiles = M > 0 ? w_pairs * ch.n_chunks : 0;
@@ -867,6 +935,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         if (EPI == kEpiQkvRope) {
           epilogue_rope_block(v, epi, scratch, quarter, lane, (n_warp0 - quarter * 32) / 128, tok_base + c, tok_limit);
+        } else if (EPI == kEpiArgmax) {
+          epilogue_argmax_block(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N);
         } else {
           epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok);
           epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
@@ -883,14 +953,56 @@ __global__ void __launch_bounds__(kThreads, 1)
   // MMAs of the pair are in flight: meet at a cluster barrier first.
   tc_fence_before();
   __syncthreads();
-  if (timing) {
-    atomicAdd(timing, (unsigned long long)(global_ns() - t_begin));
-    atomicAdd(timing + 1, 2ull * (unsigned long long)M * (unsigned long long)N * (unsigned long long)K);
-  }
+  RD_TIMING_END(M, N, K);
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kMaxChunk) : "memory");
+  }
+}
+
+// Second half of the fused LM-head argmax: 32 tokens per block, 8 groups of threads walk the slices of a
+// token in ascending order (coalesced over the tokens), then the groups are combined; equal logits keep
+// the smaller vocabulary id.
+__global__ void __launch_bounds__(256) argmax_merge_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
+                                                           int64_t ld, int n_slices, int m_max, const int32_t* __restrict__ m_dev,
+                                                           int32_t* __restrict__ out32, int64_t* __restrict__ out64) {
+  rd::pdl_launch_dependents();
+  rd::pdl_wait();
+  const int M = rd::live_rows(m_dev, m_max);
+  const int t = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int tok = blockIdx.x * 32 + t;
+  if (blockIdx.x * 32 >= M) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  if (tok < M) {
+    for (int sl = g; sl < n_slices; sl += 8) {
+      const float v = part_val[(int64_t)sl * ld + tok];
+      const int id = part_idx[(int64_t)sl * ld + tok];
+      if (v > best || (v == best && id < bi)) {
+        best = v;
+        bi = id;
+      }
+    }
+  }
+  __shared__ float sb[8][32];
+  __shared__ int si[8][32];
+  sb[g][t] = best;
+  si[g][t] = bi;
+  __syncthreads();
+  if (g == 0 && tok < M) {
+#pragma unroll
+    for (int o = 1; o < 8; ++o) {
+      const float v = sb[o][t];
+      const int id = si[o][t];
+      if (v > best || (v == best && id < bi)) {
+        best = v;
+        bi = id;
+      }
+    }
+    if (bi == 0x7fffffff) bi = 0;
+    if (out32) out32[tok] = bi;
+    if (out64) out64[tok] = bi;
   }
 }
 
@@ -987,6 +1099,8 @@ int launch_epi(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t
     case RD_EPI_RES: return launch_out<RD_EPI_RES>(p, out_dtype, e, m_dev, status, s);
     case RD_EPI_SWIGLU: return launch_out<RD_EPI_SWIGLU>(p, out_dtype, e, m_dev, status, s);
     case kEpiQkvRope: return launch_out<kEpiQkvRope>(p, out_dtype, e, m_dev, status, s);
+    case kEpiArgmax: return launch_out<kEpiArgmax>(p, out_dtype, e, m_dev, status, s);
+    case kEpiSliceMax: return launch_out<kEpiSliceMax>(p, out_dtype, e, m_dev, status, s);
     default: return RD_ERR_ARG;
   }
 }
@@ -1057,9 +1171,58 @@ extern "C" int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, 
   return launch_epi(p, RD_BF16, e, m_dev, kEpiQkvRope, status, (cudaStream_t)stream);
 }
 
-extern "C" int rd_gemm_set_timing(void* acc) {
+static inline int64_t part_ld_of(int m_max) { return ((int64_t)m_max + 31) / 32 * 32; }
+
+extern "C" int64_t rd_gemm_argmax_workspace_bytes(int m_max, int N) {
+  if (m_max < 1 || N < 1) return 0;
+  return (int64_t)((N + 31) / 32) * part_ld_of(m_max) * 8;
+}
+
+extern "C" int rd_gemm_bf16_tc_argmax(const void* plan, const int32_t* m_dev, void* workspace, int64_t workspace_bytes,
+                                      int32_t* out32, int64_t* out64, int32_t* status, void* stream) {
+  RD_REQUIRE(plan && workspace && (out32 || out64), RD_ERR_ARG);
+  const GemmPlan* p = static_cast<const GemmPlan*>(plan);
+  RD_REQUIRE(((uintptr_t)workspace & 15) == 0, RD_ERR_ALIGN);
+  RD_REQUIRE(workspace_bytes >= rd_gemm_argmax_workspace_bytes(p->m_max, p->N), RD_ERR_CAPACITY);
+  const int n_slices = (p->N + 31) / 32;
+  const int64_t ld = part_ld_of(p->m_max);
+  EpiArgs e{};
+  e.part_val = (float*)workspace;
+  e.part_idx = (int32_t*)((float*)workspace + (int64_t)n_slices * ld);
+  e.part_ld = ld;
+  e.C = workspace;  // no output matrix; kept non-null and aligned for the checks the epilogues share
+  e.ldc = 4;
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc = launch_epi(p, RD_F32, e, m_dev, kEpiArgmax, status, s);
+  if (rc != RD_OK) return rc;
+  cudaError_t err = rd::launch_chained(argmax_merge_kernel, dim3((p->m_max + 31) / 32), dim3(256), 0, s, 1, (const float*)e.part_val,
+                                       (const int32_t*)e.part_idx, ld, n_slices, p->m_max, m_dev, out32, out64);
+  RD_CHECK_CHAINED(err);
+  return RD_OK;
+}
+
+extern "C" int rd_gemm_bf16_tc_slicemax(const void* plan, int out_dtype, void* C, int64_t ldc, const int32_t* m_dev,
+                                        float* slice_max, int64_t slice_ld, int32_t* status, void* stream) {
+  RD_REQUIRE(plan && C && slice_max, RD_ERR_ARG);
+  RD_REQUIRE(out_dtype == RD_F32 || out_dtype == RD_BF16, RD_ERR_DTYPE);
+  const GemmPlan* p = static_cast<const GemmPlan*>(plan);
+  RD_REQUIRE(p->N % 32 == 0 && slice_ld >= p->m_max, RD_ERR_SIZE);
+  const int esz = out_dtype == RD_F32 ? 4 : 2;
+  // the slice maxima are formed on the vector store path only
+  RD_REQUIRE(((uintptr_t)C & 15) == 0 && (ldc * esz) % 16 == 0, RD_ERR_ALIGN);
+  EpiArgs e{};
+  e.C = C;
+  e.ldc = ldc;
+  e.part_val = slice_max;
+  e.part_ld = slice_ld;
+  return launch_epi(p, out_dtype, e, m_dev, kEpiSliceMax, status, (cudaStream_t)stream);
+}
+
+#ifdef RD_GEMM_TIMING
+extern "C" __attribute__((visibility("default"))) int rd_gemm_set_timing(void* acc) {
   unsigned long long* p = static_cast<unsigned long long*>(acc);
   cudaError_t err = cudaMemcpyToSymbol(g_gemm_timing, &p, sizeof(p));
   RD_CHECK_CHAINED(err);
   return RD_OK;
 }
+#endif

@@ -378,15 +378,26 @@ extern "C" int rd_cache_unpack_static(int dtype, void* cache, int NL, int B, int
   RD_REQUIRE(NL >= 1 && B >= 1 && nkv >= 1 && hd >= 1 && S >= 0 && n_flat >= 1 && S + n_flat <= max_len &&
                  (int64_t)B * nkv <= 65535 && NL * 2 <= 65535,
              RD_ERR_SIZE);
-  const size_t esz = dtype == RD_F32 ? 4 : 2;
-  const size_t need = (size_t)NL * 2 * B * nkv * n_flat * hd * esz;
-  RD_REQUIRE(need <= (size_t)RD_STATIC_SCRATCH_BYTES, RD_ERR_CAPACITY);
+  {
+    // bytes gathered = NL*2 * B*nkv * n_flat * hd * element size; the product is formed factor by factor
+    // and refused as soon as it passes the capacity, so it cannot wrap around
+    const unsigned long long cap = (unsigned long long)RD_STATIC_SCRATCH_BYTES;
+    unsigned long long need = dtype == RD_F32 ? 4ull : 2ull;
+    const unsigned long long factors[4] = {(unsigned long long)NL * 2ull, (unsigned long long)B * (unsigned long long)nkv,
+                                           (unsigned long long)n_flat, (unsigned long long)hd};
+    for (int i = 0; i < 4; ++i) {
+      RD_REQUIRE(factors[i] <= cap, RD_ERR_CAPACITY);
+      need *= factors[i];  // both operands <= 2^24 here: no overflow
+      RD_REQUIRE(need <= cap, RD_ERR_CAPACITY);
+    }
+  }
   int dev = -1;
   cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess || dev < 0 || dev >= 64) {
+  if (err != cudaSuccess || dev < 0) {
     rd_set_last_cuda_error((int)err);
     return RD_ERR_LAUNCH;
   }
+  RD_REQUIRE(dev < 64, RD_ERR_UNSUPPORTED);  // the address table below holds 64 device ordinals
   if (g_static_scratch_addr[dev] == nullptr) {
     void* p = nullptr;
     err = cudaGetSymbolAddress(&p, g_static_unpack_scratch);

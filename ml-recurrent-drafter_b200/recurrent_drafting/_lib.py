@@ -30,7 +30,7 @@ SIGNATURES = {
     "rd_abi_version": (_I, []),
     "rd_tree_pack": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P]),
     "rd_tree_pack_reference_layout": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P]),
-    "rd_drafter_prepare": (_I, [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "rd_drafter_prepare": (_I, [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "rd_vocab_topk": (_I, [_I, _P, _L, _I, _P, _I, _I, _F, _I, _F, _P, _P, _P, _P, _P]),
     "rd_beam_select": (_I, [_I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "rd_drafter_dense_log_probs": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
@@ -39,7 +39,10 @@ SIGNATURES = {
     "rd_gemm_plan_destroy": (None, [_P]),
     "rd_gemm_bf16_tc": (_I, [_P, _I, _P, _L, _P, _P, _L, _P, _I, _P, _P]),
     "rd_gemm_bf16_tc_qkv_rope": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
-    "rd_gemm_set_timing": (_I, [_P]),
+    "rd_gemm_argmax_workspace_bytes": (_L, [_I, _I]),
+    "rd_gemm_bf16_tc_argmax": (_I, [_P, _P, _P, _L, _P, _P, _P, _P]),
+    "rd_gemm_bf16_tc_slicemax": (_I, [_P, _I, _P, _L, _P, _P, _L, _P, _P]),
+    "rd_vocab_topk_sliced": (_I, [_I, _P, _L, _I, _P, _I, _I, _F, _I, _F, _P, _L, _P, _P, _P, _P, _P]),
     "rd_embed_gather": (_I, [_I, _P, _P, _P, _I, _P, _I, _P]),
     "rd_rmsnorm": (_I, [_I, _P, _P, _P, _I, _P, _I, _F, _P]),
     "rd_rope_kv_write": (_I, [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P]),

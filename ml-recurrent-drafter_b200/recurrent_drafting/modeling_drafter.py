@@ -57,8 +57,16 @@ class SparseLogProbs:
 
 
 def vocab_topk(logits: torch.Tensor, out: SparseLogProbs, subtract_max: bool, temperature: float = 1.0,
-               rows_dev: Optional[torch.Tensor] = None, top_k: int = TOP_K, mask_value: float = LOG_0) -> SparseLogProbs:
+               rows_dev: Optional[torch.Tensor] = None, top_k: int = TOP_K, mask_value: float = LOG_0,
+               slice_max: Optional[torch.Tensor] = None) -> SparseLogProbs:
+    """Sparse log-softmax(warp(logits)) rows.  slice_max [V/32, >= rows], when the GEMM that produced the
+    logits also wrote it, lets the kernel read only the slices that can hold kept entries."""
     rows, V = logits.shape
+    if slice_max is not None:
+        _lib.call("rd_vocab_topk_sliced", _lib.dtype_code(logits.dtype), _lib.ptr(logits), logits.stride(0), rows, _lib.ptr(rows_dev),
+                  V, min(top_k, V), mask_value, int(subtract_max), float(temperature), _lib.ptr(slice_max), slice_max.stride(0),
+                  _lib.ptr(out.val), _lib.ptr(out.idx), _lib.ptr(out.cnt), _lib.ptr(out.masked), _lib.stream())
+        return out
     _lib.call("rd_vocab_topk", _lib.dtype_code(logits.dtype), _lib.ptr(logits), logits.stride(0), rows, _lib.ptr(rows_dev), V,
               min(top_k, V), mask_value, int(subtract_max), float(temperature), _lib.ptr(out.val), _lib.ptr(out.idx),
               _lib.ptr(out.cnt), _lib.ptr(out.masked), _lib.stream())
@@ -181,12 +189,12 @@ class Drafter(torch.nn.Module):
 
     def _lin(self):
         if self._packed is None:
-            if not self.config.rnn:
-                raise NotImplementedError("only the recurrent (rnn=True) drafter is implemented")
             R = self.config.num_draft_layers
             self._packed = {
-                # [emb | state] @ [rnn_w | rnn_u]^T + b_u  == rnn_w(emb) + rnn_u(state)
-                "rnn": _Linear(torch.cat([self.rnn_w.weight, self.rnn_u.weight], dim=1).contiguous(), self.rnn_u.bias),
+                # [emb | state] @ [rnn_w | rnn_u]^T + b_u  == rnn_w(emb) + rnn_u(state); a drafter built with
+                # rnn=False has no such projections (its state update is embedding + state)
+                "rnn": _Linear(torch.cat([self.rnn_w.weight, self.rnn_u.weight], dim=1).contiguous(), self.rnn_u.bias)
+                if self.config.rnn else None,
                 "res": [_Linear(self.lm_head[r].linear.weight, self.lm_head[r].linear.bias) for r in range(R)],
                 "vocab": _Linear(self.lm_head[R].weight),
                 "proj": _Linear(self.input_proj.weight, self.input_proj.bias) if hasattr(self, "input_proj") else None,
@@ -206,6 +214,8 @@ class Drafter(torch.nn.Module):
                 "x": e(M, 2 * H),
                 "y": [e(M, E), e(M, E), e(M, E)],
                 "logits": e(M, V),
+                # per-(32 vocabulary ids, row) maxima written by the vocabulary GEMM's epilogue
+                "slice_max": e(V // 32, (M + 31) // 32 * 32, d=torch.float32) if V % 32 == 0 else None,
                 "q": [new_sparse(M, dev) for _ in range(Lb - 1)],
                 "q_first": new_sparse(B, dev),  # the first iteration's lists, one per batch row
                 "score": [e(B, W, d=torch.float32), e(B, W, d=torch.float32)],
@@ -257,7 +267,7 @@ class Drafter(torch.nn.Module):
         for k in range(Lb - 1):
             bin_, bout = ws["beams"][k % 2], ws["beams"][(k + 1) % 2]
             _lib.call("rd_drafter_prepare", code, _lib.ptr(embeddings.weight), _lib.ptr(bin_), _lib.ptr(ws["parent"]),
-                      _lib.ptr(ctx), _lib.ptr(a), _lib.ptr(x), B, W, Lb, H, k, st)
+                      _lib.ptr(ctx), _lib.ptr(a), _lib.ptr(x), B, W, Lb, H, k, 0 if cfg.rnn else 1, st)
             # In the first iteration every beam of a row holds the same token, state and context
             # (modeling_drafter.py:170-177), so the W rows of a batch row are identical: compute row 0
             # of each (a view with row stride W) and copy its results to the others.
@@ -266,7 +276,10 @@ class Drafter(torch.nn.Module):
             a_k, x_k, ys, logits_k = a[rows], x[rows], [y[rows] for y in ws["y"]], ws["logits"][rows]
             q_k = ws["q_first"] if shared else ws["q"][k]
             # recurrent update, written into the state half of x
-            lin["rnn"](a_k, x_k[:, H:], _lib.EPI_BIAS_SILU, ldc=x_k.stride(0))
+            if lin["rnn"] is not None:
+                lin["rnn"](a_k, x_k[:, H:], _lib.EPI_BIAS_SILU, ldc=x_k.stride(0))
+            else:
+                x_k[:, H:].copy_(a_k[:, H:])  # the prepare kernel already formed embedding + parent state
             cur = x_k
             yi = 0
             if lin["proj"] is not None:
@@ -276,8 +289,12 @@ class Drafter(torch.nn.Module):
                 nxt = ys[yi % 3]
                 res(cur, nxt, _lib.EPI_BIAS_SILU_RES, residual=cur)
                 cur, yi = nxt, yi + 1
-            lin["vocab"](cur, logits_k)
-            vocab_topk(logits_k, q_k, subtract_max=True)
+            smax = ws["slice_max"]
+            if smax is not None and not shared and lin["vocab"].with_slice_max(cur, logits_k, smax):
+                vocab_topk(logits_k, q_k, subtract_max=True, slice_max=smax)
+            else:
+                lin["vocab"](cur, logits_k)
+                vocab_topk(logits_k, q_k, subtract_max=True)
             if shared:
                 q = ws["q"][0]
                 K = q.val.shape[1]

@@ -31,11 +31,18 @@ class _Linear:
         self.bias = bias
         self._plans: Dict[Tuple, int] = {}
 
+    MAX_PLANS = 32  # distinct (activation buffer, row capacity) pairs remembered per weight
+
+    def drop_plans(self) -> None:
+        plans, self._plans = self._plans, {}
+        if plans:
+            lib = _lib.load()
+            for p in plans.values():
+                lib.rd_gemm_plan_destroy(p)
+
     def __del__(self):
         try:
-            lib = _lib.load()
-            for p in self._plans.values():
-                lib.rd_gemm_plan_destroy(p)
+            self.drop_plans()
         except Exception:
             pass
 
@@ -57,6 +64,8 @@ class _Linear:
             plan = _lib.load().rd_gemm_plan_create(_lib.ptr(a), lda, m_max, _lib.ptr(self.weight), self.weight.stride(0), n, k)
             if not plan:
                 raise _lib.RedrafterError("rd_gemm_plan_create failed (TMA descriptor could not be encoded)")
+            if len(self._plans) >= self.MAX_PLANS:
+                self.drop_plans()
             self._plans[key] = plan
         return plan
 
@@ -71,6 +80,31 @@ class _Linear:
         _lib.call("rd_gemm_bf16_tc_qkv_rope", plan, _lib.ptr(m_dev), _lib.ptr(q_out), _lib.ptr(k_cache), _lib.ptr(v_cache),
                   _lib.ptr(tok_row), _lib.ptr(tok_pos), _lib.ptr(tok_slot), _lib.ptr(cos), _lib.ptr(sin), cos.shape[0], nh, nkv,
                   hd, k_cache.shape[2], _lib.ptr(status), _lib.stream())
+
+    def argmax(self, a: torch.Tensor, out32: torch.Tensor, workspace: torch.Tensor, m_dev, m_max: int,
+               status: Optional[torch.Tensor]) -> None:
+        """out32[t] = argmax_n (a[t] . weight[n]) without materialising the product: the arg-max rides on
+        the GEMM's epilogue (rd_gemm_bf16_tc_argmax); tensor-core path only."""
+        if not self._tc_ok(a, a.stride(0)):
+            raise _lib.RedrafterError("the fused LM-head arg-max needs the tensor-core GEMM path (bf16, aligned operands)")
+        plan = self._plan(a, a.stride(0), m_max)
+        _lib.call("rd_gemm_bf16_tc_argmax", plan, _lib.ptr(m_dev), _lib.ptr(workspace), workspace.numel(), _lib.ptr(out32), None,
+                  _lib.ptr(status), _lib.stream())
+
+    def with_slice_max(self, a: torch.Tensor, c: torch.Tensor, slice_max: torch.Tensor, m_dev=None, m_max: Optional[int] = None,
+                       status: Optional[torch.Tensor] = None) -> bool:
+        """c = a W^T plus the per-(32 outputs, row) maxima of c in slice_max [N/32, >= m_max]
+        (rd_gemm_bf16_tc_slicemax).  Returns False, doing nothing, when the shapes rule it out."""
+        n, k = self.weight.shape
+        m_max = a.shape[0] if m_max is None else m_max
+        esz = 4 if c.dtype == torch.float32 else 2
+        if not (self._tc_ok(a, a.stride(0)) and n % 32 == 0 and c.data_ptr() % 16 == 0 and (c.stride(0) * esz) % 16 == 0
+                and slice_max.shape[0] * 32 == n and slice_max.stride(0) >= m_max):
+            return False
+        plan = self._plan(a, a.stride(0), m_max)
+        _lib.call("rd_gemm_bf16_tc_slicemax", plan, _lib.dtype_code(c.dtype), _lib.ptr(c), c.stride(0), _lib.ptr(m_dev),
+                  _lib.ptr(slice_max), slice_max.stride(0), _lib.ptr(status), _lib.stream())
+        return True
 
     def __call__(self, a: torch.Tensor, c: torch.Tensor, epilogue: int = _lib.EPI_NONE, residual=None,
                  m_dev: Optional[torch.Tensor] = None, lda: Optional[int] = None, ldc: Optional[int] = None,
@@ -151,10 +185,13 @@ class LlamaForCausalLM(nn.Module):
         self.lm_head.weight.requires_grad_(False)
         self.model.embed_tokens.weight.requires_grad_(False)
         self._ws: Dict[Tuple, Dict[str, torch.Tensor]] = {}
+        self._ws_full: Optional[Dict[str, torch.Tensor]] = None
+        self._ws_cap: Tuple[int, int] = (0, 0)
         self._linears = None
         self._rope = None
         self._attn_plans: Dict[Tuple, int] = {}
         self._attn_split_ws: Optional[torch.Tensor] = None
+        self._head_ws: Optional[torch.Tensor] = None
         self.gemm_status: Optional[torch.Tensor] = None
 
     # ----------------------------------------------------------------- reference-compatible surface
@@ -263,7 +300,10 @@ class LlamaForCausalLM(nn.Module):
     def _invalidate(self):
         self._linears = None
         self._ws = {}
+        self._ws_full = None
+        self._ws_cap = (0, 0)
         self._rope = None
+        self._head_ws = None
         self._drop_attn_plans()
 
     def _drop_attn_plans(self):
@@ -292,7 +332,7 @@ class LlamaForCausalLM(nn.Module):
                 plan = _lib.load().rd_attention_plan_create(_lib.ptr(q), m_max, _lib.ptr(kc), _lib.ptr(vc), batch, nh, nkv, hd, max_len)
                 if not plan:
                     raise _lib.RedrafterError("rd_attention_plan_create failed (TMA descriptor could not be encoded)")
-                if len(self._attn_plans) > 4096:
+                if len(self._attn_plans) >= 4 * self.n_layers:
                     self._drop_attn_plans()
                 self._attn_plans[key] = plan
             shares = attention.key_range_shares(batch, nh, max_new, max_kv)
@@ -330,24 +370,43 @@ class LlamaForCausalLM(nn.Module):
         return self._rope
 
     def workspace(self, m_max: int, logit_rows: int) -> Dict[str, torch.Tensor]:
+        """Activation buffers for m_max packed tokens and fp32 logits for logit_rows rows.  One
+        grow-only set is kept (sized by the largest request seen); smaller requests get leading
+        slices of it, so a process that serves prompts of many different sizes holds one set, not
+        one per size.  When the set grows, the descriptors tied to the old buffers are dropped."""
         key = (m_max, logit_rows)
         ws = self._ws.get(key)
-        if ws is None:
-            H, dt, dev = self.config.hidden_size, self.dtype, self.device
-            nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
-            e = lambda *s, d=dt: torch.empty(*s, dtype=d, device=dev)  # noqa: E731
-            ws = {
-                "h": e(m_max, H),
-                "xn": e(m_max, H),
-                "qkv": e(m_max, (nh + 2 * nkv) * hd),
-                "q": e(m_max, nh * hd),
-                "attn": e(m_max, nh * hd),
-                "act": e(m_max, self.config.intermediate_size),
-                "hidden": e(m_max, H),
-                "logits": e(logit_rows, self.config.vocab_size, d=torch.float32),
-            }
-            self._ws[key] = ws
+        if ws is not None:
+            return ws
+        H, dt, dev = self.config.hidden_size, self.dtype, self.device
+        nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        cap_m, cap_l = self._ws_cap
+        full = dict(self._ws_full or {})
+        if m_max > cap_m:
+            cap_m = m_max
+            for name, width in (("h", H), ("xn", H), ("qkv", (nh + 2 * nkv) * hd), ("q", nh * hd), ("attn", nh * hd),
+                                ("act", self.config.intermediate_size), ("hidden", H)):
+                full[name] = torch.empty(cap_m, width, dtype=dt, device=dev)
+        if logit_rows > cap_l:
+            cap_l = logit_rows
+            full["logits"] = torch.empty(cap_l, self.config.vocab_size, dtype=torch.float32, device=dev)
+        if (cap_m, cap_l) != self._ws_cap:
+            self._ws_full, self._ws_cap = full, (cap_m, cap_l)
+            self._ws = {}
+            self._drop_plans()
+        ws = {k: (v[:logit_rows] if k == "logits" else v[:m_max]) for k, v in full.items()}
+        if len(self._ws) >= 16:
+            self._ws.pop(next(iter(self._ws)))
+        self._ws[key] = ws
         return ws
+
+    def _drop_plans(self) -> None:
+        """Forgets every TMA descriptor set (GEMM and attention plans); they are rebuilt on demand."""
+        if self._linears is not None:
+            for group in self._linears.values():
+                for lin in (group if isinstance(group, list) else [group]):
+                    lin.drop_plans()
+        self._drop_attn_plans()
 
     def backbone(self, ws, cache_tensor: torch.Tensor, m_max: int, m_dev, tok_ids, tok_row, tok_pos, tok_slot, row_start,
                  kv_begin, base_len, batch: int, max_new: int, max_kv: int, mode: int, tree_mask=None, mask_words: int = 0,
@@ -394,6 +453,40 @@ class LlamaForCausalLM(nn.Module):
         """fp32 logits of the given hidden rows (modeling_llama.py:272)."""
         self._lin()["head"](hidden_rows, logits, _lib.EPI_NONE, m_dev=m_dev, status=self.gemm_status)
         return logits
+
+    def fused_head_ok(self) -> bool:
+        """The LM head can run with the arg-max or the slice maxima in its epilogue (bf16 tensor-core path,
+        vocabulary a multiple of 32)."""
+        return self.dtype == torch.bfloat16 and self.config.hidden_size % 64 == 0 and self.config.vocab_size % 32 == 0
+
+    def _head_scratch(self, rows: int) -> torch.Tensor:
+        """fp32 [vocab/32, rows rounded up to 32] scratch of the fused LM-head epilogues, grow-only."""
+        slices = (self.config.vocab_size + 31) // 32
+        ld = (rows + 31) // 32 * 32
+        if self._head_ws is None or self._head_ws.shape[1] < ld:
+            self._head_ws = torch.empty(2 * slices, ld, dtype=torch.float32, device=self.device)
+        return self._head_ws
+
+    def lm_argmax(self, hidden_rows: torch.Tensor, out32: torch.Tensor, m_dev=None) -> None:
+        """Greedy tokens of the given hidden rows, int32, without writing the logits (modeling_llama.py:272 +
+        recurrent_drafting.py:52)."""
+        rows = hidden_rows.shape[0]
+        ws = self._head_scratch(rows)
+        need = _lib.load().rd_gemm_argmax_workspace_bytes(rows, self.config.vocab_size)
+        flat = ws.view(-1).view(torch.uint8)
+        assert flat.numel() >= need
+        self._lin()["head"].argmax(hidden_rows, out32, flat, m_dev, rows, self.gemm_status)
+
+    def lm_logits_with_slice_max(self, hidden_rows: torch.Tensor, logits: torch.Tensor, m_dev=None) -> Optional[torch.Tensor]:
+        """lm_logits() that also returns the [vocab/32, rows'] slice maxima for rd_vocab_topk_sliced, or None
+        (plain logits computed) when the fused epilogue does not apply."""
+        rows = hidden_rows.shape[0]
+        if self.fused_head_ok():
+            smax = self._head_scratch(rows)[: self.config.vocab_size // 32]
+            if self._lin()["head"].with_slice_max(hidden_rows, logits, smax, m_dev=m_dev, status=self.gemm_status):
+                return smax
+        self.lm_logits(hidden_rows, logits, m_dev=m_dev)
+        return None
 
     # ----------------------------------------------------------------- reference forward
     @torch.inference_mode()

@@ -10,9 +10,11 @@ One step enqueues, without reading anything back:
   -> acceptance + commit of the accepted path's tokens, K/V rows and next-step inputs.
 Then one small device->host copy (row lengths, accepted counts) sizes the yielded tensor.
 
-Cache rows never move: row b keeps the left offset the prompt's padding gave it
-(kv_begin[b]) and only grows (kv_len[b]).  The reference re-right-aligns every row after each step;
-its slot numbering is available in index space through reference_commit_slots().
+Cache rows never move and are stored left-compacted: the first real token of row b sits in slot
+kv_begin[b] = 0 whatever the prompt's left padding, and the row only grows (kv_len[b]).  The furthest
+slot a step can write is therefore max_b kv_len[b] + W*Lb, which the reference's allocation
+(max_length + W*Lb) always covers.  The reference re-right-aligns every row after each step; its
+slot numbering is available in index space through reference_commit_slots().
 """
 from dataclasses import dataclass
 from typing import Generator, Optional, Tuple
@@ -85,6 +87,7 @@ class RecurrentDrafting(torch.nn.Module):
         self.llm = llm
         self.drafter = drafter
         self.last_state: Optional[_DecodeState] = None
+        self.last_cache: Optional[kv_cache.Cache] = None
 
     def llm_n_kv_heads(self) -> int:
         if isinstance(self.llm, modeling_llama.LlamaForCausalLM):
@@ -116,11 +119,11 @@ class RecurrentDrafting(torch.nn.Module):
         tok_ids = input_ids[live].contiguous()
         M = tok_ids.numel()
         tok_row = torch.arange(B, device=dev)[:, None].expand(B, Lp)[live].to(torch.int32)
-        tok_slot = cols[live].to(torch.int32)
         tok_pos = (cols - pads[:, None])[live].to(torch.int32)
+        tok_slot = tok_pos  # rows are stored without their left padding: slot = position
         row_start = torch.zeros(B + 1, dtype=torch.int32, device=dev)
         row_start[1:] = torch.cumsum(n_new, 0).to(torch.int32)
-        st.kv_begin.copy_(pads.to(torch.int32))
+        st.kv_begin.zero_()
         base_len = torch.zeros(B, dtype=torch.int32, device=dev)
         ws = llm.workspace(M, B)
         hidden = llm.backbone(ws, cache._cache, M, None, tok_ids, tok_row, tok_pos, tok_slot, row_start, st.kv_begin,
@@ -138,7 +141,8 @@ class RecurrentDrafting(torch.nn.Module):
             _lib.call("rd_sample_from_sparse", _lib.ptr(sp.val), _lib.ptr(sp.idx), _lib.ptr(sp.cnt), B, _lib.ptr(u),
                       _lib.ptr(st.init_tok), _lib.stream())
         st.kv_len.copy_(n_new.to(torch.int32))
-        st.token_buf[:, :Lp] = input_ids
+        # the same compaction for the token ids: column c of row b holds input_ids[b, pads[b] + c]
+        st.token_buf[:, :Lp] = torch.gather(input_ids, 1, (cols + pads[:, None]).clamp_(max=Lp - 1))
         for k, v in cache.sliced:
             k.length = v.length = Lp
         return int(n_new.max().item())
@@ -164,12 +168,23 @@ class RecurrentDrafting(torch.nn.Module):
                 hidden = llm.backbone(ws, cache_t, m_max, fp.m_dev, fp.tokens, fp.tok_row, fp.tok_pos, fp.tok_slot,
                                       fp.row_start, st.kv_begin, fp.base_len, B, W * Lb, s_max + W * Lb, _lib.ATTN_TREE,
                                       tree_mask=fp.tree_mask, mask_words=fp.mask_words, n_pos=max_len + 1)
-                logits = llm.lm_logits(hidden, ws["logits"], m_dev=fp.m_dev)
+                fused_head = llm.fused_head_ok()
+                smax = None
+                if sampling_args.greedy and fused_head:
+                    # the arg-max over the vocabulary rides on the LM head's epilogue: no logits are written
+                    llm.lm_argmax(hidden, st.llm_tok, m_dev=fp.m_dev)
+                    logits = ws["logits"]
+                elif sampling_args.greedy:
+                    logits = llm.lm_logits(hidden, ws["logits"], m_dev=fp.m_dev)
+                else:
+                    logits = ws["logits"]
+                    smax = llm.lm_logits_with_slice_max(hidden, logits, m_dev=fp.m_dev)
         V = logits.shape[1]
         with rec.time("accept_candidate_tokens"):
             if sampling_args.greedy:
-                _lib.call("rd_argmax_rows", _lib.ptr(logits), logits.stride(0), m_max, _lib.ptr(fp.m_dev), V,
-                          _lib.ptr(st.llm_tok), None, sm)
+                if not fused_head:
+                    _lib.call("rd_argmax_rows", _lib.ptr(logits), logits.stride(0), m_max, _lib.ptr(fp.m_dev), V,
+                              _lib.ptr(st.llm_tok), None, sm)
                 _lib.call("rd_accept_commit_greedy", code, _lib.ptr(draft.beams), B, W, Lb, _lib.ptr(fp.unpacker),
                           _lib.ptr(fp.row_start), _lib.ptr(st.llm_tok), _lib.ptr(hidden), H, _lib.ptr(cache_t), NL, nkv,
                           max_len, hd, _lib.ptr(st.kv_begin), _lib.ptr(fp.base_len), _lib.ptr(st.kv_len),
@@ -177,7 +192,7 @@ class RecurrentDrafting(torch.nn.Module):
                           _lib.ptr(st.ctx), sm)
             else:
                 modeling_drafter.vocab_topk(logits, st.p, subtract_max=False, temperature=sampling_args.temperature,
-                                            rows_dev=fp.m_dev)
+                                            rows_dev=fp.m_dev, slice_max=smax)
                 u = torch.rand(B, W, Lb - 1, device=logits.device)
                 u_next = torch.rand(B, device=logits.device)
                 q = draft.q
@@ -213,6 +228,8 @@ class RecurrentDrafting(torch.nn.Module):
         st = _DecodeState(llm, B, W, Lb, max_length + Lb * W, dev)
         llm.gemm_status = st.status
         self.last_state = st
+        self.last_cache = cache
+        assert max_length + Lb * W <= st.token_buf.shape[1] == cache._cache.shape[4]
         s_max = self._comprehend_prompt(st, cache, input_ids, sampling_args, special_tokens.pad)
         ref_len = seq_len  # the reference's padded sequence length S before the step
         while seq_len < max_length:
@@ -224,6 +241,8 @@ class RecurrentDrafting(torch.nn.Module):
                     raise _lib.RedrafterError(
                         f"a tensor-core kernel gave up waiting on its pipeline (status {int(st.small_host[2, 0])})")
                 s_max = int(st.small_host[0].max())
+                # rows are left-compacted, so the next step writes at most W*Lb slots past the longest row
+                assert s_max + W * Lb <= st.token_buf.shape[1] or s_max + 1 >= max_length
                 out = torch.empty(B, s_max + 1, dtype=torch.int64, device=dev)
                 _lib.call("rd_emit_tokens", _lib.ptr(st.token_buf), st.token_buf.shape[1], _lib.ptr(st.kv_begin),
                           _lib.ptr(st.kv_len), _lib.ptr(st.init_tok), int(special_tokens.pad), B, s_max + 1, _lib.ptr(out),

@@ -5,6 +5,7 @@ independent process per GPU, recurrent_drafting/benchmark/perf_wrt_candidates/ru
 helpers here are the only places where ranks talk: splitting the batch, and one final gather of
 the generated tokens and per-rank statistics (NCCL over NVLink on GPUs, gloo in the CPU tests).
 """
+from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
 import torch
@@ -49,3 +50,69 @@ def reduce_stats(elapsed_ms: float, generated_tokens: float, accepted_tokens: fl
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     dist.all_reduce(n, op=dist.ReduceOp.SUM, group=group)
     return float(t[0]), float(n[0]), float(n[1])
+
+
+
+@dataclass
+class ShardedResult:
+    """What generate_sharded() returns on every rank."""
+
+    tokens: Optional[torch.Tensor]  # rank `dst` only: (n_requests, length) int64, rows in request order, left-padded
+    generated_local: int  # tokens this rank generated for its rows (the first token, from the prefill, included)
+    steps_local: int  # decode steps this rank ran
+    d2h_bytes: int  # bytes copied to host_sink
+
+
+def _left_pads(tokens: torch.Tensor, pad_id: int) -> torch.Tensor:
+    return torch.sum(torch.cumprod(torch.eq(tokens, pad_id).to(torch.int64), dim=-1), dim=-1)
+
+
+def generate_sharded(model, input_ids_all: torch.Tensor, max_length: int, beam_shape, sampling_args, special_tokens,
+                     device=None, max_steps: Optional[int] = None, host_sink: Optional[torch.Tensor] = None, dst: int = 0,
+                     group=None, ledger=None) -> ShardedResult:
+    """One batch of requests in, one token matrix out, on however many ranks the process group has.
+
+    Every rank is given the same (n_requests, prompt_len) int64 matrix (host or device memory), decodes
+    the rows shard_bounds() assigns to it with `model.generate` until max_length (or for max_steps
+    decode steps), and rank `dst` receives all rows back in request order.  The only communication is
+    the final gather.  Without an initialised process group the call runs as a single rank.  The
+    reference spreads requests over GPUs by starting one process per GPU from a shell script
+    (recurrent_drafting/benchmark/perf_wrt_candidates/run.bash:28-50); this is that, as one call.
+
+    host_sink, if given, is a pinned (rows, >= max_length + 1) int64 host tensor that receives every
+    yielded matrix (the per-step read-back a serving loop does)."""
+    from . import stats
+
+    if dist.is_available() and dist.is_initialized():
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+    else:
+        rank, world = 0, 1
+    lo, hi = shard_bounds(input_ids_all.shape[0], rank, world)
+    local = input_ids_all[lo:hi]
+    if device is not None:
+        local = local.to(device, non_blocking=True)
+    pad = int(special_tokens.pad)
+    out, steps, d2h = None, 0, 0
+    if hi > lo:
+        gen = model.generate(ledger if ledger is not None else stats.Ledger(), local, max_length, beam_shape, sampling_args,
+                             special_tokens)
+        try:
+            for out in gen:
+                steps += 1
+                if host_sink is not None:
+                    host_sink[: out.shape[0], : out.shape[1]].copy_(out, non_blocking=True)
+                    d2h += out.numel() * out.element_size()
+                    if out.is_cuda:
+                        torch.cuda.current_stream(out.device).synchronize()
+                if max_steps is not None and steps >= max_steps:
+                    break
+        finally:
+            gen.close()
+    if out is None:  # a rank without rows, or max_length already reached by the prompt
+        out = local
+    generated = int(((out.shape[1] - _left_pads(out, pad)) - (local.shape[1] - _left_pads(local, pad))).sum()) if hi > lo else 0
+    if world == 1:
+        return ShardedResult(out, generated, steps, d2h)
+    parts = gather_tokens(out, pad, dst=dst, group=group)
+    tokens = torch.cat(parts, dim=0) if parts is not None else None
+    return ShardedResult(tokens, generated, steps, d2h)

@@ -111,3 +111,57 @@ def zipf_beams(batch: int, width: int, length: int, vocab: int, seed: int, a: fl
                     children[key] = np.clip(rs.zipf(a, size=branch) + 2, 3, vocab - 1)
                 out[b, i, j] = children[key][min(rs.zipf(a) - 1, branch - 1)]
     return out
+
+
+# A model pair with PLANTED acceptance, so that decode steps accept 0 .. Lb-1 draft tokens in a known
+# pattern (random-init pairs accept nothing).  The LLM's output projections of attention and MLP are zero,
+# so its residual stream stays the token embedding and its LM head maps token t to f(t); the drafter maps
+# token t to g(t) through its recurrent state; f is one cycle over the ids [3, V), g equals f except on the
+# ids in `wrong`, where the draft is rejected.
+PLANTED_LLAMA = dict(hidden_size=64, num_attention_heads=2, num_key_value_heads=2, num_hidden_layers=2, intermediate_size=96,
+                     vocab_size=200, rms_norm_eps=1e-6, rope_theta=10000.0)
+PLANTED_DRAFTER = dict(vocab_size=200, hidden_size=64, exit_dim=128, num_draft_layers=1, rnn=True)
+
+
+def planted_models(seed: int = 5, n_wrong: int = 30):
+    """Returns (llama weights, drafter weights, cycle): cycle[i+1] = f(cycle[i]); the drafter's guess
+    after cycle[2*i] (i < n_wrong) is wrong."""
+    lcfg, dcfg = PLANTED_LLAMA, PLANTED_DRAFTER
+    rs = np.random.RandomState(seed)
+    V, H = lcfg["vocab_size"], lcfg["hidden_size"]
+    lw = llama_weights(lcfg, seed)
+    for l in range(lcfg["num_hidden_layers"]):
+        lw[f"model.layers.{l}.self_attn.o_proj.weight"][:] = 0
+        lw[f"model.layers.{l}.mlp.down_proj.weight"][:] = 0
+    lw["model.norm.weight"][:] = 1
+    emb = rs.standard_normal((V, H)).astype(np.float32)
+    lw["model.embed_tokens.weight"] = emb
+    cycle = 3 + rs.permutation(V - 3)
+    f = {int(cycle[i]): int(cycle[(i + 1) % len(cycle)]) for i in range(len(cycle))}
+    g = dict(f)
+    for i in range(n_wrong):
+        tkn = int(cycle[2 * i])
+        g[tkn] = int(cycle[(2 * i + 7) % len(cycle)])  # some other id than f(tkn)
+    head = np.zeros((V, H), dtype=np.float32)
+    for tkn, nxt in f.items():
+        head[nxt] = emb[tkn]
+    lw["lm_head.weight"] = head
+    dw = drafter_weights(dcfg, seed + 1)
+    E = dcfg["exit_dim"]
+    dw["lm_head.0.linear.weight"][:] = 0
+    dw["lm_head.0.linear.bias"][:] = 0
+    dw["rnn_u.weight"][:] = 0
+    dw["rnn_u.bias"][:] = 0
+    dw["rnn_w.weight"] = (2.0 * np.eye(H)).astype(np.float32)
+    x = 2.0 * emb
+    state = (x / (1.0 + np.exp(-x))).astype(np.float32)  # silu(rnn_w e_t): the state after reading token t
+    centred = state - state[3:].mean(axis=0, keepdims=True)
+    vocab = np.zeros((V, E), dtype=np.float32)
+    # several tokens may share a wrong guess; the later assignment wins, which only moves where drafts fail
+    for tkn, nxt in g.items():
+        vocab[nxt, H:] = centred[tkn]
+    for tkn, nxt in f.items():
+        if g[tkn] == nxt:
+            vocab[nxt, H:] = centred[tkn]
+    dw["lm_head.1.weight"] = vocab
+    return lw, dw, cycle

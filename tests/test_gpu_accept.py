@@ -130,13 +130,16 @@ def test_greedy_accept_commit_vs_oracle(dtype, B, W, L):
     assert np.array_equal(sl[:, :, 2], plan["dst_slot"])
 
 
+@pytest.mark.parametrize("B,W,L,V", [(4, 6, 5, 300), (16, 16, 5, 32000)])
 @pytest.mark.parametrize("temp", [1.0, 0.6])
-def test_sampling_accept_vs_oracle(temp):
+def test_sampling_accept_vs_oracle(temp, B, W, L, V):
+    """Speculative-sampling acceptance, residual resampling and commit against the oracle with the
+    same injected uniforms; the second shape is the sampling benchmark's (batch 16, 16 beams of 5,
+    vocabulary 32000: recurrent_drafting.py:499-556, 271-343)."""
     import recurrent_drafting as rd
     from recurrent_drafting import _lib
 
     md = rd.modeling_drafter
-    B, W, L, V = 4, 6, 5, 300
     sc = _scenario(B, W, L, seed=11, V=V)
     rs = sc["rs"]
     beams, unp, starts = sc["beams"], sc["unp"], sc["starts"]

@@ -172,3 +172,81 @@ def test_qkv_projection_with_fused_rope_equals_projection_then_rope():
     assert torch.equal(q1, q2) and torch.equal(k1, k2) and torch.equal(v1, v2)
     assert torch.all(q2[live:] == 5.0), "rows beyond the live count were written"
     assert (q2[:live] != 5.0).any() and (k2 != 6.0).any() and (v2 != 7.0).any()
+
+
+@pytest.mark.parametrize("M,N,K,live", [(1800, 32000, 512, 761), (360, 32000, 256, None), (300, 1000, 128, None), (64, 320, 64, 5),
+                                        (1800, 32000, 256, 0)])
+def test_lm_head_with_argmax_in_the_epilogue(M, N, K, live):
+    """rd_gemm_bf16_tc_argmax: the tokens equal the row arg-max of the fp32 logits the plain LM-head GEMM
+    writes (same accumulators), ties included: duplicated weight rows give exactly equal logits, inside one
+    32-id slice, across slices and across weight tiles, and the smaller id must win."""
+    from recurrent_drafting import _lib
+    from recurrent_drafting.modeling_llama import _Linear
+
+    g = torch.Generator(device="cuda").manual_seed(N + K)
+    a = (torch.randn(M, K, generator=g, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.1).bfloat16()
+    # a dominant direction shared by a few rows, so that the duplicates ARE the maxima of many tokens
+    w[7] = w[7] * 6
+    for dup in (9, 40, N - 3):
+        w[dup] = w[7]
+    w[N // 2] = w[N // 2] * 6
+    w[N // 2 + 300 if N // 2 + 300 < N else N - 1] = w[N // 2]
+    lin = _Linear(w)
+    m_dev = None if live is None else torch.tensor([live], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    logits = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    lin(a, logits, m_dev=m_dev, status=status)
+    need = _lib.load().rd_gemm_argmax_workspace_bytes(M, N)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    out = torch.full((M,), -7, dtype=torch.int32, device="cuda")
+    lin.argmax(a, out, ws, m_dev, M, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    n_live = M if live is None else live
+    want = logits[:n_live].cpu().numpy().argmax(axis=-1)  # numpy: first index among equals
+    got = out.cpu().numpy()
+    assert np.array_equal(got[:n_live], want)
+    assert (got[n_live:] == -7).all(), "rows beyond the live count were written"
+    if n_live >= 100:
+        assert np.isin(want, [7, N // 2]).mean() > 0.2, "the planted ties never decided a row"
+    # a workspace that is too small is refused on the host
+    small = torch.empty(max(need // 2, 16), dtype=torch.uint8, device="cuda")
+    with pytest.raises(_lib.RedrafterError):
+        lin.argmax(a, out, small, m_dev, M, status)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K,live", [(360, 32000, 512, None), (1280, 32000, 256, 1000), (45, 1024, 128, None)])
+def test_slice_maxima_and_sliced_topk_equal_the_plain_path(out_dtype, M, N, K, live):
+    """rd_gemm_bf16_tc_slicemax writes the same matrix as the plain GEMM plus exact per-slice maxima, and
+    rd_vocab_topk_sliced returns what rd_vocab_topk returns, bit for bit (tie rows included)."""
+    import recurrent_drafting as rd
+    from recurrent_drafting.modeling_llama import _Linear
+
+    md = rd.modeling_drafter
+    g = torch.Generator(device="cuda").manual_seed(N + K + M)
+    a = (torch.randn(M, K, generator=g, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.1).bfloat16()
+    w[100] = w[3]  # exactly tied columns
+    w[N - 1] = w[3]
+    lin = _Linear(w)
+    m_dev = None if live is None else torch.tensor([live], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    plain = torch.zeros(M, N, dtype=out_dtype, device="cuda")
+    lin(a, plain, m_dev=m_dev, status=status)
+    fused = torch.zeros(M, N, dtype=out_dtype, device="cuda")
+    smax = torch.full((N // 32, (M + 31) // 32 * 32), float("nan"), dtype=torch.float32, device="cuda")
+    assert lin.with_slice_max(a, fused, smax, m_dev=m_dev, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    n_live = M if live is None else live
+    assert torch.equal(plain, fused)
+    want_max = fused[:n_live].float().reshape(n_live, N // 32, 32).max(dim=-1).values.T
+    assert torch.equal(smax[:, :n_live], want_max)
+    for subtract, temp in ((True, 1.0), (False, 0.7)):
+        p0 = md.vocab_topk(plain, md.new_sparse(M, "cuda"), subtract_max=subtract, temperature=temp, rows_dev=m_dev)
+        p1 = md.vocab_topk(fused, md.new_sparse(M, "cuda"), subtract_max=subtract, temperature=temp, rows_dev=m_dev, slice_max=smax)
+        torch.cuda.synchronize()
+        for x, y in ((p0.val, p1.val), (p0.idx, p1.idx), (p0.cnt, p1.cnt), (p0.masked, p1.masked)):
+            assert torch.equal(x[:n_live], y[:n_live])
