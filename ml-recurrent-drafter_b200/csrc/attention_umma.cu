@@ -1,9 +1,10 @@
 // Tree-masked flash attention on the 5th-generation tensor cores (head_dim 128, bf16).
 //
 // One CTA serves 128 queries of one (batch row, head): normally every packed tree token of the row.
-//   warps 0, 6  TMA producers (one elected lane each): warp 0 loads the Q tile once and then the K
-//               tiles of 64 keys, warp 6 the V tiles (two 64-column boxes each, 128-byte swizzle, no
-//               multicast), each into its own two-stage ring.  A K stage is free as soon as QK^T of
+//   warps 0, 6  TMA producers (one elected lane each): warp 0 loads the K tiles of 64 keys, warp 6 the V
+//               tiles (two 64-column boxes each, 128-byte swizzle, no multicast), each into its own
+//               two-stage ring; the Q tile and the first two K and V tiles are requested by thread 0 as
+//               soon as the barriers exist, before the TMEM allocation.  A K stage is free as soon as QK^T of
 //               its tile is done, a V stage after PV; the producers wait on the same completion
 //               barriers the softmax uses (one commit per product);
 //   warp 1      MMA issuer (one elected thread):
@@ -35,7 +36,6 @@ constexpr int HD = 128;
 constexpr int BMQ = 128;  // queries per CTA
 constexpr int BNK = 64;   // keys per tile
 constexpr int kThreads = 224;
-constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int kSubTile = 64 * 128;            // bytes of a [64 rows x 64 bf16] box = 8 KB
 constexpr int kQBytes = BMQ * HD * 2;         // 32 KB: two [128 x 64] boxes
 constexpr int kKVStage = 2 * BNK * HD * 2;    // 32 KB: K (2 boxes) then V (2 boxes)
@@ -78,15 +78,33 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// One attempt: the hardware may suspend the thread until the phase completes or a time limit of its own
+// expires, so a waiter costs no issue slots while it waits and wakes as soon as the barrier flips.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait (one second).  Returns false when it gave up or when another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) {
-      if (*abort_flag) return false;
-      __nanosleep(32);
-    }
+  if (mbar_test(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > 1000000000ull) return false;
   }
-  return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
@@ -173,6 +191,12 @@ __global__ void __launch_bounds__(kThreads, 2)
                           int n_split, float* __restrict__ partial) {
   const int b = blockIdx.z, h = blockIdx.y;
   rd::pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    // the descriptors are kernel parameters: their fetch may start before the dependency wait
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
   rd::pdl_wait();  // row_start, Q and the new K/V rows come from the kernels before this one
   const int rs = row_start[b];
   const int n_new = row_start[b + 1] - rs;
@@ -227,6 +251,26 @@ __global__ void __launch_bounds__(kThreads, 2)
     mbar_init(p_full, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // The first loads (Q and the first ring's worth of K and V tiles) go out here, before the TMEM
+    // allocation and the block-wide barrier below: a short chain of key tiles spends a large part of its
+    // life waiting for this first data.
+    mbar_expect_tx(q_full, kQBytes);
+    tma_load_2d(sQ, &map_q, q_full, h * HD, rs + q0);
+    tma_load_2d(sQ + BMQ * 128, &map_q, q_full, h * HD + 64, rs + q0);
+    for (int t = 0; t < kStages && t < n_tiles; ++t) {
+      const int row = kv_row0 + (t_begin + t) * BNK;
+      uint8_t* dk = sKV + t * kKVStage;
+      mbar_expect_tx(&k_full[t], 2 * kSubTile);
+      tma_load_2d(dk, &map_k, &k_full[t], 0, row);
+      tma_load_2d(dk + kSubTile, &map_k, &k_full[t], 64, row);
+    }
+    for (int t = 0; t < kStages && t < n_tiles; ++t) {
+      const int row = kv_row0 + (t_begin + t) * BNK;
+      uint8_t* dv = sKV + t * kKVStage + 2 * kSubTile;
+      mbar_expect_tx(&v_full[t], 2 * kSubTile);
+      tma_load_2d(dv, &map_v, &v_full[t], 0, row);
+      tma_load_2d(dv + kSubTile, &map_v, &v_full[t], 64, row);
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
@@ -242,20 +286,15 @@ __global__ void __launch_bounds__(kThreads, 2)
     // ---------------- TMA producers: warp 0 = Q and the K ring, warp 6 = the V ring ----------------
     if (lane == 0) {
       const bool is_k = warp == 0;
-      if (is_k) {
-        mbar_expect_tx(q_full, kQBytes);
-        tma_load_2d(sQ, &map_q, q_full, h * HD, rs + q0);
-        tma_load_2d(sQ + BMQ * 128, &map_q, q_full, h * HD + 64, rs + q0);
-      }
       uint64_t* full = is_k ? k_full : v_full;
       // a stage is free when the product that read it is done: QK^T of tile t-2 for K, PV of tile t-2
       // for V.  Each of these barriers completes once per two tiles, so a parity wait is unambiguous.
       uint64_t* done = is_k ? s_full : o_full;
       const CUtensorMap* map = is_k ? &map_k : &map_v;
       bool ok = true;
-      for (int t = 0; ok && t < n_tiles; ++t) {
+      for (int t = kStages; ok && t < n_tiles; ++t) {  // tiles 0 .. kStages-1 were requested at set-up
         const int s = t & 1;
-        if (t >= kStages && !mbar_wait(&done[s], ((t - 2) >> 1) & 1, abort_flag)) {
+        if (!mbar_wait(&done[s], ((t - 2) >> 1) & 1, abort_flag)) {
           ok = false;
           break;
         }

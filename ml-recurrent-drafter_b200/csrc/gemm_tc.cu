@@ -410,7 +410,8 @@ __device__ __forceinline__ void epilogue_argmax_block(const float* v, const EpiA
   }
   __syncwarp();  // the scratch is reused by the next block
   const int tok = tok0 + lane;
-  if (tok < tok_limit) {
+  // a ragged last weight tile reaches past N: slices that hold no vocabulary id have no slot in the workspace
+  if (tok < tok_limit && n_warp0 < N) {
     const int64_t at = (int64_t)(n_warp0 >> 5) * e.part_ld + tok;
     e.part_val[at] = best;
     e.part_idx[at] = n_warp0 + bj;
