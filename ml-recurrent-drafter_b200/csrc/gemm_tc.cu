@@ -153,7 +153,10 @@ __device__ __forceinline__ uint32_t umma_instr_desc(int n) {
 // Token chunking shared by all roles: n_chunks equal chunks of `chunk` tokens (a multiple of 16).
 // The fewest chunks that respect the 256-token MMA limit are used unless that leaves compute units
 // (CTAs or CTA pairs) idle: a GEMM with few weight tiles (N = 4096) then cuts the tokens finer so
-// that about one tile exists per unit.
+// that about one tile exists per unit.  Finer chunks than that cost more than they balance: every
+// chunk re-reads its weight tile from L2, and the kernel is sensitive to that operand traffic (gate/up
+// at 761 tokens: 115 us with 3 chunks of 256 in 3.5 rounds of tiles, 135 us with 4 of 192, 150 us with
+// 6 of 128, although both leave fewer idle tile slots).
 struct Chunking {
   int n_chunks, chunk;
 };
@@ -228,8 +231,8 @@ struct EpiArgs {
   const float* sin_t;
   int n_pos, nh, nkv, max_len;
   // kEpiArgmax / kEpiSliceMax only: per (32-feature slice, token) partial results, laid out [slice][part_ld]
-  float* part_val;
-  int32_t* part_idx;
+  float* part_val;               // kEpiSliceMax: largest stored value
+  unsigned long long* part_key;  // kEpiArgmax: (order-preserving key of the largest logit) << 32 | ~(first id holding it)
   int64_t part_ld;
 };
 
@@ -412,9 +415,11 @@ __device__ __forceinline__ void epilogue_argmax_block(const float* v, const EpiA
   const int tok = tok0 + lane;
   // a ragged last weight tile reaches past N: slices that hold no vocabulary id have no slot in the workspace
   if (tok < tok_limit && n_warp0 < N) {
-    const int64_t at = (int64_t)(n_warp0 >> 5) * e.part_ld + tok;
-    e.part_val[at] = best;
-    e.part_idx[at] = n_warp0 + bj;
+    // one 64-bit word per (slice, token): larger logit first, then the smaller id, under plain unsigned order
+    // (-0 and +0 compare equal as floats, so both take +0's key)
+    if (best == 0.f) best = 0.f;
+    e.part_key[(int64_t)(n_warp0 >> 5) * e.part_ld + tok] =
+        ((unsigned long long)rd::float_key(best) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)(n_warp0 + bj));
   }
 }
 
@@ -962,48 +967,37 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-// Second half of the fused LM-head argmax: 32 tokens per block, 8 groups of threads walk the slices of a
-// token in ascending order (coalesced over the tokens), then the groups are combined; equal logits keep
-// the smaller vocabulary id.
-__global__ void __launch_bounds__(256) argmax_merge_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
-                                                           int64_t ld, int n_slices, int m_max, const int32_t* __restrict__ m_dev,
-                                                           int32_t* __restrict__ out32, int64_t* __restrict__ out64) {
+// Second half of the fused LM-head argmax: the partial results are 64-bit keys whose unsigned order is
+// (logit descending, id ascending), so the merge is a plain maximum.  A block serves 8 tokens with 32
+// groups of threads walking the slices (each 32-byte sector of the [slice][token] array is read once).
+constexpr int kMergeTok = 8, kMergeGroups = 32;
+__global__ void __launch_bounds__(kMergeTok* kMergeGroups) argmax_merge_kernel(const unsigned long long* __restrict__ part_key, int64_t ld,
+                                                                              int n_slices, int m_max,
+                                                                              const int32_t* __restrict__ m_dev,
+                                                                              int32_t* __restrict__ out32, int64_t* __restrict__ out64) {
   rd::pdl_launch_dependents();
   rd::pdl_wait();
   const int M = rd::live_rows(m_dev, m_max);
-  const int t = threadIdx.x & 31, g = threadIdx.x >> 5;
-  const int tok = blockIdx.x * 32 + t;
-  if (blockIdx.x * 32 >= M) return;
-  float best = -INFINITY;
-  int bi = 0x7fffffff;
+  if ((int)blockIdx.x * kMergeTok >= M) return;
+  const int t = threadIdx.x % kMergeTok, g = threadIdx.x / kMergeTok;
+  const int tok = blockIdx.x * kMergeTok + t;
+  unsigned long long best = 0ull;
   if (tok < M) {
-    for (int sl = g; sl < n_slices; sl += 8) {
-      const float v = part_val[(int64_t)sl * ld + tok];
-      const int id = part_idx[(int64_t)sl * ld + tok];
-      if (v > best || (v == best && id < bi)) {
-        best = v;
-        bi = id;
-      }
+#pragma unroll 4
+    for (int sl = g; sl < n_slices; sl += kMergeGroups) {
+      const unsigned long long k = part_key[(int64_t)sl * ld + tok];
+      best = k > best ? k : best;
     }
   }
-  __shared__ float sb[8][32];
-  __shared__ int si[8][32];
-  sb[g][t] = best;
-  si[g][t] = bi;
+  __shared__ unsigned long long sk[kMergeGroups][kMergeTok];
+  sk[g][t] = best;
   __syncthreads();
   if (g == 0 && tok < M) {
 #pragma unroll
-    for (int o = 1; o < 8; ++o) {
-      const float v = sb[o][t];
-      const int id = si[o][t];
-      if (v > best || (v == best && id < bi)) {
-        best = v;
-        bi = id;
-      }
-    }
-    if (bi == 0x7fffffff) bi = 0;
-    if (out32) out32[tok] = bi;
-    if (out64) out64[tok] = bi;
+    for (int o = 1; o < kMergeGroups; ++o) best = sk[o][t] > best ? sk[o][t] : best;
+    const int id = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+    if (out32) out32[tok] = id;
+    if (out64) out64[tok] = id;
   }
 }
 
@@ -1188,16 +1182,15 @@ extern "C" int rd_gemm_bf16_tc_argmax(const void* plan, const int32_t* m_dev, vo
   const int n_slices = (p->N + 31) / 32;
   const int64_t ld = part_ld_of(p->m_max);
   EpiArgs e{};
-  e.part_val = (float*)workspace;
-  e.part_idx = (int32_t*)((float*)workspace + (int64_t)n_slices * ld);
+  e.part_key = (unsigned long long*)workspace;
   e.part_ld = ld;
   e.C = workspace;  // no output matrix; kept non-null and aligned for the checks the epilogues share
   e.ldc = 4;
   cudaStream_t s = (cudaStream_t)stream;
   int rc = launch_epi(p, RD_F32, e, m_dev, kEpiArgmax, status, s);
   if (rc != RD_OK) return rc;
-  cudaError_t err = rd::launch_chained(argmax_merge_kernel, dim3((p->m_max + 31) / 32), dim3(256), 0, s, 1, (const float*)e.part_val,
-                                       (const int32_t*)e.part_idx, ld, n_slices, p->m_max, m_dev, out32, out64);
+  cudaError_t err = rd::launch_chained(argmax_merge_kernel, dim3((p->m_max + kMergeTok - 1) / kMergeTok), dim3(kMergeTok * kMergeGroups), 0,
+                                       s, 1, (const unsigned long long*)e.part_key, ld, n_slices, p->m_max, m_dev, out32, out64);
   RD_CHECK_CHAINED(err);
   return RD_OK;
 }

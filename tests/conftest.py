@@ -53,3 +53,8 @@ def g_acc():
 @pytest.fixture(scope="session")
 def g_model():
     return load_golden("model_cases")
+
+
+@pytest.fixture(scope="session")
+def g_variants():
+    return load_golden("drafter_variants")

@@ -339,6 +339,19 @@ def model_cases(rd, out):
     out["gen_samp_lengths"] = np.array([s.shape[1] for s in steps])
 
 
+def drafter_variants(rd, out):
+    """Beam search of a drafter built with rnn=False and an input projection (modeling_drafter.py:112-115, 196)."""
+    llm, dr = build_ref_models(rd, mb.NANO_LLAMA, mb.NANO_DRAFTER_NO_RNN, 41)
+    rs = np.random.RandomState(42)
+    B, H, V = 2, mb.NANO_LLAMA["hidden_size"], mb.NANO_LLAMA["vocab_size"]
+    state = rs.standard_normal((B, H)).astype(np.float32)
+    tok = rs.randint(3, V, size=(B,)).astype(np.int64)
+    with torch.inference_mode():
+        beams, logq = dr.beam_search_candidates(_t(state), _t(tok), llm.get_input_embeddings(), rd.modeling_drafter.BeamShape(6, 4))
+    out["nornn_state"], out["nornn_tok"] = state, tok
+    out["nornn_beams"], out["nornn_logq"] = _np(beams), _np(logq)
+
+
 def main():
     if len(sys.argv) != 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <checkout of apple/ml-recurrent-drafter>")
@@ -353,6 +366,7 @@ def main():
         (pack_cases, "pack_cases"),
         (acceptance_cases, "acceptance_cases"),
         (model_cases, "model_cases"),
+        (drafter_variants, "drafter_variants"),
     ]:
         out = {}
         fn(rd, out)

@@ -33,6 +33,9 @@ NANO_LLAMA = dict(
     rope_theta=10000.0,
 )
 NANO_DRAFTER = dict(vocab_size=320, hidden_size=64, exit_dim=128, num_draft_layers=2, rnn=True)
+# the drafter variants the reference also supports: no recurrent projections (state = embedding + state) and an
+# input projection (exit_dim != 2 * hidden_size)
+NANO_DRAFTER_NO_RNN = dict(vocab_size=320, hidden_size=64, exit_dim=96, num_draft_layers=1, rnn=False)
 
 
 def llama_weights(cfg: Dict, seed: int, std: float = 0.05) -> Dict[str, np.ndarray]:
@@ -79,9 +82,10 @@ def drafter_weights(cfg: Dict, seed: int, std: float = 0.05) -> Dict[str, np.nda
         w[f"lm_head.{r}.linear.weight"] = n(E, E)
         w[f"lm_head.{r}.linear.bias"] = n(E)
     w[f"lm_head.{R}.weight"] = n(V, E)
-    w["rnn_u.weight"] = n(H, H)
-    w["rnn_u.bias"] = n(H)
-    w["rnn_w.weight"] = n(H, H)
+    if cfg.get("rnn", True):
+        w["rnn_u.weight"] = n(H, H)
+        w["rnn_u.bias"] = n(H)
+        w["rnn_w.weight"] = n(H, H)
     return w
 
 

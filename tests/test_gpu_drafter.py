@@ -51,6 +51,19 @@ def test_beam_search_fp32_vs_reference_fixture(g_model):
     np.testing.assert_allclose(logq.cpu().numpy(), g_model["bs_logq"], rtol=1e-4, atol=2e-4)
 
 
+def test_beam_search_without_recurrent_projections_vs_reference_fixture(g_variants):
+    """A drafter built with rnn=False (state = embedding + state) and an input projection: beams equal to the
+    reference's, log-probs within fp32 noise."""
+    import recurrent_drafting as rd
+
+    llm, dr, lw, dw = build_models(mb.NANO_LLAMA, mb.NANO_DRAFTER_NO_RNN, 41)
+    assert not hasattr(dr, "rnn_u") and hasattr(dr, "input_proj")
+    beams, logq = dr.beam_search_candidates(t(g_variants["nornn_state"]), t(g_variants["nornn_tok"]), llm.get_input_embeddings(),
+                                            rd.modeling_drafter.BeamShape(6, 4))
+    assert np.array_equal(beams.cpu().numpy(), g_variants["nornn_beams"])
+    np.testing.assert_allclose(logq.cpu().numpy(), g_variants["nornn_logq"], rtol=1e-4, atol=2e-4)
+
+
 @pytest.mark.parametrize("B,W,Lb", [(2, 4, 3), (3, 45, 5), (1, 50, 2), (2, 16, 8)])
 def test_beam_search_fp32_vs_oracle(B, W, Lb):
     import recurrent_drafting as rd

@@ -113,6 +113,18 @@ def test_beam_search_differential(g_model):
     np.testing.assert_allclose(logq, g_model["bs_logq"], rtol=1e-4, atol=1e-4)
 
 
+def test_beam_search_without_recurrent_projections(g_variants):
+    """The rnn=False drafter with an input projection (modeling_drafter.py:112-115, 196), fixture from the reference."""
+    lw = mb.llama_weights(mb.NANO_LLAMA, 41)
+    cfg = mb.NANO_DRAFTER_NO_RNN
+    dw = mb.drafter_weights(cfg, 42)
+    assert "rnn_u.weight" not in dw and "input_proj.weight" in dw
+    beams, logq = drafter.beam_search_candidates(dw, cfg["num_draft_layers"], g_variants["nornn_state"], g_variants["nornn_tok"],
+                                                 lw["model.embed_tokens.weight"], 6, 4, rnn=False)
+    assert np.array_equal(beams, g_variants["nornn_beams"])
+    np.testing.assert_allclose(logq, g_variants["nornn_logq"], rtol=1e-4, atol=1e-4)
+
+
 def test_llama_forward_differential(g_model):
     lw = mb.llama_weights(mb.NANO_LLAMA, 31)
     dw = mb.drafter_weights(mb.NANO_DRAFTER, 32)
