@@ -65,7 +65,7 @@ WORKLOADS = {
     "c4": "c4: Vicuna-13B-arch greedy decode, 8 requests per GPU, random-init weights",
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of the four GEMMs of one verify layer (down, QKV, o, gate/up), mean per launch
-GEMM_TRAFFIC_BYTES_PER_LAUNCH = int((113.2 + 3.8 + 109.4 + 4.7 + 45.8 + 0.1 + 191.5 + 12.5) / 4 * 1e6)
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = int((113.2 + 4.7 + 108.5 + 4.4 + 45.8 + 0.1 + 191.2 + 14.6) / 4 * 1e6)
 
 
 def metric_name(cfg_name: str) -> str:

@@ -789,6 +789,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   rd::pdl_launch_dependents();  // the next kernel may set itself up while this one runs
+  if (threadIdx.x == 0) {
+    // the descriptors are kernel parameters: their fetch may start before the dependency wait
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -824,8 +829,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;

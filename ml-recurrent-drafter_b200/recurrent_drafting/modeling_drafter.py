@@ -10,6 +10,7 @@ log-softmax with sparse output -> cross-beam top-W and beam reorder.  The (batch
 log-prob tensor of the reference is never materialised on the decode path; it is rebuilt from the
 sparse lists only when a caller asks for it.
 """
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -289,7 +290,7 @@ class Drafter(torch.nn.Module):
                 nxt = ys[yi % 3]
                 res(cur, nxt, _lib.EPI_BIAS_SILU_RES, residual=cur)
                 cur, yi = nxt, yi + 1
-            smax = ws["slice_max"]
+            smax = ws["slice_max"] if os.environ.get("RD_FUSED_HEAD", "1") != "0" else None
             if smax is not None and not shared and lin["vocab"].with_slice_max(cur, logits_k, smax):
                 vocab_topk(logits_k, q_k, subtract_max=True, slice_max=smax)
             else:

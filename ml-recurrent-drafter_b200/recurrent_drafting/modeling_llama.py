@@ -457,7 +457,8 @@ class LlamaForCausalLM(nn.Module):
     def fused_head_ok(self) -> bool:
         """The LM head can run with the arg-max or the slice maxima in its epilogue (bf16 tensor-core path,
         vocabulary a multiple of 32)."""
-        return self.dtype == torch.bfloat16 and self.config.hidden_size % 64 == 0 and self.config.vocab_size % 32 == 0
+        return (self.dtype == torch.bfloat16 and self.config.hidden_size % 64 == 0 and self.config.vocab_size % 32 == 0
+                and os.environ.get("RD_FUSED_HEAD", "1") != "0")
 
     def _head_scratch(self, rows: int) -> torch.Tensor:
         """fp32 [vocab/32, rows rounded up to 32] scratch of the fused LM-head epilogues, grow-only."""

@@ -109,6 +109,49 @@ def test_beam_search_bf16_tolerance():
     assert same >= B * W // 2, same
 
 
+def test_beam_search_bf16_vocabulary_32000_teacher_forced():
+    """The drafter at the benchmark's routing (bf16 tcgen05 GEMMs, exit_dim 1024 with two residual blocks,
+    vocabulary head of 32000 with slice maxima + sliced top-k, 45 beams of 5) against the fp32 oracle holding
+    the same bf16-rounded weights.  bf16 beams are not pinned (near-ties reorder), so the oracle is teacher-forced
+    along the GPU's own beams: a beam's tokens determine its recurrent state, hence the log-softmax row every one
+    of its positions was drawn from; those rows must agree where both sides keep the entry."""
+    import recurrent_drafting as rd
+    from gpu_helpers import HD128_DRAFTER, HD128_LLAMA
+
+    llm, dr, lw, dw = build_models(HD128_LLAMA, HD128_DRAFTER, 77, dtype=torch.bfloat16)
+    dwr = bf16_round(dw)
+    emb = bf16_round({"e": lw["model.embed_tokens.weight"]})["e"]
+    H, V, R = HD128_DRAFTER["hidden_size"], HD128_DRAFTER["vocab_size"], HD128_DRAFTER["num_draft_layers"]
+    B, W, Lb = 2, 45, 5
+    rs = np.random.RandomState(8)
+    state = t(rs.standard_normal((B, H)).astype(np.float32)).bfloat16()
+    tok_np = rs.randint(3, V, size=(B,)).astype(np.int64)
+    beams, logq = dr.beam_search_candidates(state, t(tok_np), llm.get_input_embeddings(), rd.modeling_drafter.BeamShape(W, Lb))
+    beams, logq = beams.cpu().numpy(), logq.cpu().numpy()
+    assert np.array_equal(beams[:, :, 0], np.repeat(tok_np[:, None], W, axis=1))
+    ctx = state.float().cpu().numpy()
+    worst, overlap_min, drawn_rank_max = 0.0, 1.0, 0
+    for b in range(B):
+        for w in range(0, W, 4):  # every fourth beam keeps the oracle's share of the test short
+            s = np.zeros(H, dtype=np.float32)
+            for k in range(Lb - 1):
+                e = emb[beams[b, w, k]]
+                s = odr.silu(e @ dwr["rnn_w.weight"].T + s @ dwr["rnn_u.weight"].T + dwr["rnn_u.bias"])
+                x = np.concatenate([ctx[b], s])[None, :]
+                want = odr.log_softmax(odr.compute_logits(dwr, x, R))[0]
+                got = logq[b, w, k]
+                kept_w, kept_g = want > -40000, got > -40000
+                both = kept_w & kept_g
+                overlap_min = min(overlap_min, both.sum() / max(kept_w.sum(), 1))
+                worst = max(worst, float(np.abs(got[both] - want[both]).max()))
+                # the token the GPU drew at this position is among the oracle's best few of that row
+                drawn = beams[b, w, k + 1]
+                drawn_rank_max = max(drawn_rank_max, int((want > want[drawn]).sum()))
+    assert worst <= 0.1, worst  # log-probs in nats; bf16 activations through three 1024-wide layers (measured 0.068)
+    assert overlap_min >= 0.85, overlap_min
+    assert drawn_rank_max < W + 5, drawn_rank_max
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_vocab_topk_massive_ties(dtype):
     """Rows where thousands of entries tie at the top-k threshold (the radix-select path): the list

@@ -1,7 +1,8 @@
 """The environment switches of the library change how kernels are launched or fused, never what
 they compute: a bf16 decode loop (head_dim 128, so the tcgen05 GEMM and attention are on the path)
 must emit the same tokens with programmatic dependent launches and with ordinary launches, and with
-the rotary embedding fused into the QKV projection or as a kernel of its own.  The switches are read
+the rotary embedding fused into the QKV projection or as a kernel of its own, and with the arg-max / slice
+maxima in the LM-head and vocabulary-head epilogues or as separate passes over the logits.  The switches are read
 once per process, so every setting runs in a child process (run as a script, this file is that child)."""
 import json
 import os
@@ -12,8 +13,8 @@ import pytest
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LLAMA = dict(hidden_size=256, num_attention_heads=2, num_key_value_heads=2, num_hidden_layers=2, intermediate_size=512,
-             vocab_size=1000, rms_norm_eps=1e-5, rope_theta=10000.0)
-DRAFTER = dict(vocab_size=1000, hidden_size=256, exit_dim=512, num_draft_layers=1, rnn=True)
+             vocab_size=1024, rms_norm_eps=1e-5, rope_theta=10000.0)  # a multiple of 32: the fused heads apply
+DRAFTER = dict(vocab_size=1024, hidden_size=256, exit_dim=512, num_draft_layers=1, rnn=True)
 
 
 def _child() -> None:
@@ -34,7 +35,7 @@ def _child() -> None:
 
 def _run(env_extra):
     env = dict(os.environ)
-    for k in ("RD_PDL", "RD_FUSED_ROPE", "RD_GEMM_PAIRS"):
+    for k in ("RD_PDL", "RD_FUSED_ROPE", "RD_GEMM_PAIRS", "RD_FUSED_HEAD"):
         env.pop(k, None)
     env.update(env_extra)
     r = subprocess.run([sys.executable, os.path.abspath(__file__)], env=env, capture_output=True, text=True, timeout=600)
@@ -47,7 +48,7 @@ def _run(env_extra):
 def test_launch_and_fusion_switches_do_not_change_the_tokens():
     base = _run({})
     assert len(base) == 3 and all(len(row) == 96 for row in base)
-    for setting in ({"RD_PDL": "0"}, {"RD_FUSED_ROPE": "0"}, {"RD_GEMM_PAIRS": "0"}):
+    for setting in ({"RD_PDL": "0"}, {"RD_FUSED_ROPE": "0"}, {"RD_GEMM_PAIRS": "0"}, {"RD_FUSED_HEAD": "0"}):
         assert _run(setting) == base, setting
 
 
