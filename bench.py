@@ -15,7 +15,8 @@ ours:      `value` times K steps after W warm-up steps with the prompt already o
            (with N > 1 ranks: one batch of N x B requests split by replicas.generate_sharded and
            gathered on rank 0 inside the timed region).  `roofline` is measured live for the dominant
            kernel (the tcgen05 GEMM); `prefill` is the time to the first token; `cpu_baseline`
-           times the numpy oracle on the host cores on a bounded sample (rank 0, N = 1 only).
+           times a bounded sample (prefill + 2 decode steps) of the reference itself on the host cores in a
+           child process, or the numpy port when the reference cannot run (rank 0, N = 1 only).
 reference: the reference's own PyTorch implementation (installed under baseline/_ref, CPU, fp32) run
            through RecurrentDrafting.generate on the host cores with the same configuration, for the
            prefill and as many decode steps as fit a time budget; the numpy port on one row is
@@ -66,6 +67,20 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of the four GEMMs of one verify layer (down, QKV, o, gate/up), mean per launch
 GEMM_TRAFFIC_BYTES_PER_LAUNCH = int((113.2 + 4.7 + 108.5 + 4.4 + 45.8 + 0.1 + 191.2 + 14.6) / 4 * 1e6)
+
+
+def workload_config(cfg_name: str, world: int) -> dict:
+    """The `config` object of the JSON line; both arms describe the workload with the same keys and values."""
+    lc, R, B, W, Lb, Lp, gen, dt, greedy, temp = CONFIGS[cfg_name]
+    H, I, V, NL = lc["hidden_size"], lc["intermediate_size"], lc["vocab_size"], lc["num_hidden_layers"]
+    weight_gb = (NL * (4 * H * H + 3 * H * I) + V * H) * (2 if dt == "bf16" else 4) / 1e9
+    l2 = (f"inputs larger than L2 ({weight_gb:.1f} GB of weights are streamed every step)" if weight_gb > 0.2
+          else f"no flush: the {weight_gb * 1e3:.0f} MB of weights fit L2 (tiny configuration, launch bound)")
+    return {"workload": WORKLOADS[cfg_name], "batch_per_gpu": B, "beam_width": W, "beam_length": Lb, "prompt_len": Lp,
+            "layers": lc["num_hidden_layers"], "hidden": lc["hidden_size"], "vocab": lc["vocab_size"],
+            "sampling": "greedy" if greedy else f"temperature {temp}",
+            "parallelism": f"replicas x{world} (batch of {B * world} requests sharded by rows, no data-path collective)",
+            "l2": l2}
 
 
 def metric_name(cfg_name: str) -> str:
@@ -258,7 +273,7 @@ def run_ours(args):
         if world > 1:
             dist.destroy_process_group()
         return {"metric": metric_name(args.config), "value": round(tokens / (ms * 1e-3), 2), "unit": "tokens/s", "n_gpus": world, "steps": K,
-                "warmup": Wm, "ms_per_step": round(ms / K, 4), "impl": "ours", "config": {"workload": WORKLOADS[args.config]},
+                "warmup": Wm, "ms_per_step": round(ms / K, 4), "impl": "ours", "config": workload_config(args.config, world),
                 "gpu_launches": launches, "clocks": clocks, "note": "value only (profiling run)"} if rank == 0 else None
 
     # ---- roofline pass: event pairs around every kernel launch (C-ABI call) of a few more steps;
@@ -352,6 +367,9 @@ def run_ours(args):
                 "kernel_time_breakdown": breakdown}
 
     # ---- end to end through the public API from pinned host memory; the prefill is timed on its own inside it
+    if world > 1:
+        # first use of the collective the final gather runs on (communicator set-up is not part of a request)
+        replicas.gather_tokens(torch.zeros(1, 1, dtype=torch.int64, device=dev), 0)
     barrier()
     pf0, pf1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     real_prefill = model._comprehend_prompt
@@ -386,11 +404,7 @@ def run_ours(args):
             "metric": metric_name(args.config), "value": round(tokens / (ms * 1e-3), 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dt,
             "data": "synthetic", "impl": "ours",
-            "config": {"workload": WORKLOADS[args.config],
-                       "batch_per_gpu": B, "beam_width": W, "beam_length": Lb, "prompt_len": Lp, "layers": lc["num_hidden_layers"],
-                       "hidden": lc["hidden_size"], "vocab": lc["vocab_size"], "sampling": "greedy" if greedy else f"temperature {temp}",
-                       "parallelism": f"replicas x{world} (batch of {B * world} requests sharded by rows, no data-path collective)",
-                       "l2": "inputs larger than L2 (the weights, 13.5 GB at 7B, are streamed every step)"},
+            "config": workload_config(args.config, world),
             "accepted_tokens_per_step": round(accepted / (K * B * world), 4),
             "e2e": {"value": round(e2e_tokens / (e2e_ms * 1e-3), 2), "unit": "tokens/s", "h2d_bytes_per_step": B * Lp * 8 // K,
                     "d2h_bytes_per_step": res.d2h_bytes // K,
@@ -544,13 +558,19 @@ def reference_max_length(cfg_name: str, steps_cap: int) -> int:
     return Lp + gen if cfg_name == "c1" else Lp + (steps_cap + 2) * Lb + 8
 
 
-def reference_unavailable_reason(cfg_name: str, steps_cap: int):
-    """None when the installed reference can run this configuration in fp32 on this host."""
+def reference_unavailable_reason(cfg_name: str, steps_cap: int, sample: bool = False):
+    """None when the installed reference can run this configuration in fp32 on this host (and, for a bounded
+    sample, when its prefill is short enough for one)."""
     if not os.path.isdir(os.path.join(REF_INSTALL, "recurrent_drafting")):
         return "baseline/_ref holds no installed reference"
     lc, R, B, W, Lb, Lp, gen, dt, greedy, temp = CONFIGS[cfg_name]
     H, I, V, NL = lc["hidden_size"], lc["intermediate_size"], lc["vocab_size"], lc["num_hidden_layers"]
     params = NL * (4 * H * H + 3 * H * I) + 2 * V * H + 2 * H * H + R * 4 * H * H + 2 * H * V
+    if sample:
+        # about 2 TFLOP/s of fp32 on 16 host cores: keep the sample's prefill under a minute
+        prefill_tflop = 2.0 * B * Lp * (NL * (4 * H * H + 3 * H * I) + V * H) / 1e12
+        if prefill_tflop > 120:
+            return f"the prefill alone is {prefill_tflop:.0f} TFLOP, too long for a bounded sample on the host cores"
     cache = NL * 2 * B * lc["num_key_value_heads"] * (reference_max_length(cfg_name, steps_cap) + W * Lb) * (H // lc["num_attention_heads"])
     # weights + the cache and the copies of it the reference makes every step + unpacked logits and log-probs + slack
     need = 4 * (params + 2 * cache) + B * W * Lb * V * 4 * 6 + (4 << 30)
@@ -643,15 +663,25 @@ def run_reference_impl(cfg_name: str, max_steps: int, budget_s: float):
 def run_cpu(args, as_reference_arm: bool):
     lc, R, B, W, Lb, Lp, gen, dt, greedy, temp = CONFIGS[args.config]
     if not as_reference_arm:
-        return run_port(args.config, 3, 40.0)
+        # the GPU arm's cpu_baseline: a bounded sample of the reference itself (prefill + 2 decode steps) in a child
+        # process (its package has the same name as this repository's), or of the numpy port when that is not possible
+        cpu = None
+        if reference_unavailable_reason(args.config, 2, sample=True) is None:
+            try:
+                r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--sample", "--config", args.config],
+                                   capture_output=True, text=True, timeout=420, env={k: v for k, v in os.environ.items()
+                                                                                      if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")})
+                if r.returncode == 0:
+                    cpu = json.loads(r.stdout.strip().splitlines()[-1])["cpu_baseline"]
+            except (subprocess.TimeoutExpired, ValueError, KeyError, IndexError):
+                cpu = None
+        return cpu if cpu is not None else run_port(args.config, 3, 40.0)
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    want_steps = max(args.warmup, 1) + args.steps
-    why = reference_unavailable_reason(args.config, max(want_steps, 2))
+    want_steps = 3 if args.sample else max(args.warmup, 1) + args.steps
+    why = reference_unavailable_reason(args.config, max(want_steps, 2), sample=args.sample)
     base = {"metric": metric_name(args.config), "unit": "tokens/s", "n_gpus": world, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
-            "config": {"workload": WORKLOADS[args.config], "batch_per_gpu": B, "beam_width": W, "beam_length": Lb, "prompt_len": Lp,
-                       "layers": lc["num_hidden_layers"], "hidden": lc["hidden_size"], "vocab": lc["vocab_size"],
-                       "sampling": "greedy" if greedy else f"temperature {temp}"},
+            "config": workload_config(args.config, world),
             "gpu_launches": 0}
     if why is not None:
         cpu = run_port(args.config, want_steps, 240.0)
@@ -670,7 +700,7 @@ def run_cpu(args, as_reference_arm: bool):
            "sample": (f"the reference's RecurrentDrafting.generate (PyTorch {dt_name()} CPU, fp32) on the whole batch of {B} rows: prefill of {B}x{Lp} "
                       f"tokens ({times[0]:.1f} s with the first step), then {len(step_times)} decode step(s); weights filled in {r['build_s']:.0f} s (untimed)"),
            "first_call_s": round(times[0], 2)}
-    if args.config != "c1":
+    if args.config != "c1" and not args.sample:
         port = run_port(args.config, 2, 45.0)
         cpu["port_cross_check"] = {"ms_per_step_one_row": port["ms_per_step_one_row"], "reference_ms_per_step_per_row": round(1e3 * sum(step_times) / len(step_times) / B, 1),
                                    "note": "numpy restatement on 1 row beside the reference's per-row step time"}
@@ -694,6 +724,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sample", action="store_true", help="reference arm: bounded sample (prefill + 2 decode steps, no port cross-check)")
     ap.add_argument("--value-only", action="store_true", help="skip the roofline, end-to-end and CPU passes (profiler runs)")
     ap.add_argument("--verbose", action="store_true", help="print the per-kernel and per-GEMM-shape timing breakdown to stderr")
     args = ap.parse_args()

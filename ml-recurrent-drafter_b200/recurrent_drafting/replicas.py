@@ -35,8 +35,10 @@ def gather_tokens(tokens: torch.Tensor, pad_id: int, dst: int = 0, group=None) -
     padded = torch.full((max_rows, max_len), pad_id, dtype=torch.int64, device=tokens.device)
     if tokens.numel():
         padded[: tokens.shape[0], max_len - tokens.shape[1] :] = tokens
-    bucket = [torch.empty_like(padded) for _ in range(world)] if rank == dst else None
-    dist.gather(padded, bucket, dst=dst, group=group)
+    # an all-gather (a collective on the channels the process group already uses) rather than a gather, whose
+    # point-to-point connections NCCL sets up lazily at first use: the matrices are a few hundred KB
+    bucket = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(bucket, padded, group=group)
     if rank != dst:
         return None
     return [b[: int(s[0])] for b, s in zip(bucket, shapes)]
