@@ -224,6 +224,12 @@ class Drafter(torch.nn.Module):
                 "anc": [torch.zeros(B, W, max(Lb - 1, 1), dtype=torch.int32, device=dev) for _ in range(2)],
                 "parent": torch.zeros(B, W, dtype=torch.int32, device=dev),
             }
+            if len(self._ws) >= 4:  # a few (batch, beam shape) combinations at most stay resident
+                self._ws.pop(next(iter(self._ws)))
+                for lin in self._lin().values():
+                    for one in (lin if isinstance(lin, list) else [lin]):
+                        if one is not None:
+                            one.drop_plans()
             self._ws[key] = ws
         return ws
 
