@@ -52,6 +52,30 @@ def test_generate_greedy_fp32_equals_reference(g_model, tag, lcfg, dcfg, seed):
     assert table.avg_token_per_step >= 1.0 and table.avg_step_time > 0
 
 
+@pytest.mark.parametrize("B,W,L,Lp,gen", [(1, 1, 2, 5, 12), (1, 50, 8, 6, 20), (3, 2, 2, 9, 10), (2, 45, 5, 3, 14)])
+def test_generate_edge_beam_shapes_fp32_equal_the_oracle(B, W, L, Lp, gen):
+    """The smallest and the largest beam shapes the reference's sweeps use (one beam of two tokens; fifty beams of
+    eight, the widest search whose first iteration has no exact ties), single-row batches and prompts shorter than a
+    beam: fp32 greedy streams, accepted counts and chosen beams equal the oracle's step by step."""
+    import recurrent_drafting as rd
+
+    llm, dr, lw, dw = build_models(mb.NANO_LLAMA, mb.NANO_DRAFTER, 31)
+    model = rd.RecurrentDrafting(llm, dr)
+    prompt = mb.prompts(B, Lp, mb.NANO_LLAMA["vocab_size"], 100 + W, left_pads=[0, 2, 1][:B] if Lp > 3 else None)
+    trace = []
+    want = list(ogen.generate(lw, mb.NANO_LLAMA, dw, mb.NANO_DRAFTER["num_draft_layers"], prompt, Lp + gen, W, L, greedy=True, trace=trace))
+    got = []
+    for step, out in enumerate(model.generate(rd.stats.Ledger(), t(prompt), Lp + gen, rd.modeling_drafter.BeamShape(W, L),
+                                              rd.SamplingArgs(1.0, True), rd.SpecialTokens(0, None))):
+        st = model.last_state
+        assert np.array_equal(st.small_host[1].numpy(), trace[step]["n_tokens_in_seq"]), step
+        assert np.array_equal(st.seq_in_beam.cpu().numpy(), trace[step]["seq_in_beam"]), step
+        got.append(out.cpu().numpy())
+    assert len(got) == len(want)
+    for a, b_ in zip(got, want):
+        assert np.array_equal(a, b_)
+
+
 def test_autoregressive_equals_reference_and_redrafter(g_model):
     import recurrent_drafting as rd
 
