@@ -630,7 +630,11 @@ static int attention_tc_launch(const void* plan, void* out, const int32_t* row_s
     RD_REQUIRE(workspace_bytes >= rd_attention_split_workspace_bytes(p->m_max, p->nh, n_split), RD_ERR_CAPACITY);
   }
   auto kern = attention_umma_kernel;
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  static bool smem_set = false;  // set once, so that steady-state launches are pure launches
+  if (!smem_set) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    smem_set = true;
+  }
   dim3 grid(((max_new + BMQ - 1) / BMQ) * n_split, p->nh, p->B);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
   cudaError_t err = rd::launch_chained(kern, grid, dim3(kThreads), kSmemBytes, (cudaStream_t)stream, 1, p->map_q, p->map_k, p->map_v,

@@ -1044,7 +1044,16 @@ bool make_map(CUtensorMap* map, const void* base, int64_t ld_elems, int rows, in
 template <typename Kern>
 int launch_cluster2(Kern kern, int grid, int smem_bytes, cudaStream_t s, const GemmPlan* p, const EpiArgs& e, const int32_t* m_dev,
                     int32_t* status) {
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  // the attribute is set once per kernel (this template is shared by every kernel of the same signature), so that
+  // steady-state launches are pure launches
+  static const void* configured[64];
+  static int n_configured = 0;
+  bool seen = false;
+  for (int i = 0; i < n_configured; ++i) seen = seen || configured[i] == (const void*)kern;
+  if (!seen) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (n_configured < 64) configured[n_configured++] = (const void*)kern;
+  }
   cudaError_t err = rd::launch_chained(kern, dim3(grid), dim3(kThreads), smem_bytes, s, 2, p->map_a, p->map_w, e, p->m_max, m_dev,
                                        p->N, p->K, status);
   RD_CHECK_CHAINED(err);
@@ -1081,13 +1090,21 @@ int launch_out(const GemmPlan* p, int out_dtype, const EpiArgs& e, const int32_t
   const int grid = tiles < sm_count ? tiles : sm_count;
   if (out_dtype == RD_F32) {
     auto kern = gemm_tc_kernel<EPI, true>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    static bool smem_set = false;
+    if (!smem_set) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+      smem_set = true;
+    }
     if (rd::launch_chained(kern, dim3(grid), dim3(kThreads), L::kBytes, s, 1, p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K,
                            status) != cudaSuccess)
       return RD_ERR_LAUNCH;
   } else {
     auto kern = gemm_tc_kernel<EPI, false>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    static bool smem_set = false;
+    if (!smem_set) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+      smem_set = true;
+    }
     if (rd::launch_chained(kern, dim3(grid), dim3(kThreads), L::kBytes, s, 1, p->map_a, p->map_w, e, p->m_max, m_dev, p->N, p->K,
                            status) != cudaSuccess)
       return RD_ERR_LAUNCH;

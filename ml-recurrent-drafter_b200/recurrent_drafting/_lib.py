@@ -118,8 +118,22 @@ def check(rc: int, what: str) -> None:
         raise RedrafterError(f"{what}: {msg}{extra}")
 
 
+# kernels enqueued per entry point where that is not one; `launches` counts the kernels this process has enqueued
+# through call() (a replayed CUDA graph adds the number of kernels captured in it, see count_replay)
+KERNELS_PER_CALL = {"rd_tree_pack": 2, "rd_gemm_bf16_tc_argmax": 2, "rd_attention_tc_split": 2, "rd_cache_unpack": 2,
+                    "rd_cache_unpack_static": 2}
+launches = 0
+
+
 def call(name: str, *args) -> None:
+    global launches
+    launches += KERNELS_PER_CALL.get(name, 1)
     check(getattr(load(), name)(*args), name)
+
+
+def count_replay(n_kernels: int) -> None:
+    global launches
+    launches += n_kernels
 
 
 def ptr_array(tensors):

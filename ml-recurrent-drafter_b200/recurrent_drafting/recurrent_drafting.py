@@ -16,6 +16,8 @@ slot a step can write is therefore max_b kv_len[b] + W*Lb, which the reference's
 (max_length + W*Lb) always covers.  The reference re-right-aligns every row after each step; its
 slot numbering is available in index space through reference_commit_slots().
 """
+import contextlib
+import os
 from dataclasses import dataclass
 from typing import Generator, Optional, Tuple
 
@@ -81,11 +83,48 @@ class _DecodeState:
         self.status = self.small[2, :1]
 
 
+class _StepGraphs:
+    """The three phases of a decode step (draft, verify, accept) captured as CUDA graphs for one generate() call:
+    a step is then three graph launches instead of some 260 kernel launches, which is what bounds small batches
+    (the host needs 3-4 ms to enqueue a 7B step, a batch of one or two rows keeps the GPU busy for about as long).
+    Captured after the first eager steps, when every TMA descriptor set and workspace exists; all tensors the
+    phases touch live as long as the call, and nothing in them depends on a host value that changes per step."""
+
+    def __init__(self):
+        self.draft = self.verify = self.accept = None
+        self.ready = False
+        self.n_kernels = 0  # kernels captured in the three graphs together
+
+    def capture(self, model: "RecurrentDrafting", st: _DecodeState, cache: kv_cache.Cache, beam_shape,
+                sampling_args: "SamplingArgs") -> None:
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        graphs = [torch.cuda.CUDAGraph() for _ in range(3)]
+        before = _lib.launches
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graphs[0], stream=stream):
+                draft = model._draft_phase(st, beam_shape)
+            with torch.cuda.graph(graphs[1], stream=stream):
+                verified = model._verify_phase(st, cache, beam_shape, sampling_args, draft, 0)
+            with torch.cuda.graph(graphs[2], stream=stream):
+                model._accept_phase(st, cache, beam_shape, sampling_args, draft, verified)
+        torch.cuda.current_stream().wait_stream(stream)
+        # capturing enqueues nothing: the calls made above are the kernels of every later replay
+        self.n_kernels = _lib.launches - before
+        _lib.launches = before
+        self.draft, self.verify, self.accept = graphs
+        self.ready = True
+
+
 class RecurrentDrafting(torch.nn.Module):
-    def __init__(self, llm: modeling_llama.LlamaForCausalLM, drafter: modeling_drafter.Drafter):
+    def __init__(self, llm: modeling_llama.LlamaForCausalLM, drafter: modeling_drafter.Drafter,
+                 cuda_graphs: Optional[bool] = None):
         super().__init__()
         self.llm = llm
         self.drafter = drafter
+        # replay each phase of a decode step from a CUDA graph (greedy, bf16, head_dim 128); the environment
+        # variable RD_CUDA_GRAPHS=0/1 sets the default
+        self.cuda_graphs = (os.environ.get("RD_CUDA_GRAPHS", "1") != "0") if cuda_graphs is None else bool(cuda_graphs)
         self.last_state: Optional[_DecodeState] = None
         self.last_cache: Optional[kv_cache.Cache] = None
 
@@ -147,10 +186,48 @@ class RecurrentDrafting(torch.nn.Module):
             k.length = v.length = Lp
         return int(n_new.max().item())
 
-    def _step(self, st: _DecodeState, cache: kv_cache.Cache, beam_shape, sampling_args: SamplingArgs, s_max: int,
-              rec: stats.TextGeneration.Step) -> None:
-        """Enqueues one decode step (recurrent_drafting.py:626-679).  No host synchronisation."""
-        llm, drafter = self.llm, self.drafter
+    # One decode step = three phases that enqueue kernels and never synchronise with the host
+    # (recurrent_drafting.py:626-679).  They take and return only tensors that live as long as the generate()
+    # call, so each phase can also be captured once into a CUDA graph and replayed (see _StepGraphs).
+    def _draft_phase(self, st: _DecodeState, beam_shape) -> modeling_drafter.DraftResult:
+        return self.drafter.beam_search_sparse(st.ctx, st.init_tok, self.llm.get_input_embeddings(), beam_shape)
+
+    def _verify_phase(self, st: _DecodeState, cache: kv_cache.Cache, beam_shape, sampling_args: SamplingArgs,
+                      draft: modeling_drafter.DraftResult, s_max: int, rec=None):
+        llm = self.llm
+        B = st.kv_begin.shape[0]
+        W, Lb = beam_shape.width, beam_shape.length
+        cache_t = cache._cache
+        max_len = cache_t.shape[4]
+        fp = tree_attention.pack_flat(draft.beams, st.kv_begin, st.kv_len, out=st.fp)
+        m_max = B * W * Lb
+        ws = llm.workspace(m_max, m_max)
+        with (rec.time("base_forward") if rec is not None else contextlib.nullcontext()):
+            # On the tensor-core path the bound on the keys only decides the key-range split of the attention; it is
+            # taken from the cache's capacity there, so that every step of a request launches the same kernels.
+            # The CUDA-core attention sizes its shared memory by it and gets the tight bound.
+            tc_path = llm.dtype == torch.bfloat16 and llm.head_dim == 128
+            max_kv = max_len if tc_path else s_max + W * Lb
+            hidden = llm.backbone(ws, cache_t, m_max, fp.m_dev, fp.tokens, fp.tok_row, fp.tok_pos, fp.tok_slot,
+                                  fp.row_start, st.kv_begin, fp.base_len, B, W * Lb, max_kv, _lib.ATTN_TREE,
+                                  tree_mask=fp.tree_mask, mask_words=fp.mask_words, n_pos=max_len + 1)
+            fused_head = llm.fused_head_ok()
+            smax = None
+            if sampling_args.greedy and fused_head:
+                # the arg-max over the vocabulary rides on the LM head's epilogue: no logits are written
+                llm.lm_argmax(hidden, st.llm_tok, m_dev=fp.m_dev)
+                logits = ws["logits"]
+            elif sampling_args.greedy:
+                logits = llm.lm_logits(hidden, ws["logits"], m_dev=fp.m_dev)
+            else:
+                logits = ws["logits"]
+                smax = llm.lm_logits_with_slice_max(hidden, logits, m_dev=fp.m_dev)
+        return fp, hidden, logits, smax, fused_head
+
+    def _accept_phase(self, st: _DecodeState, cache: kv_cache.Cache, beam_shape, sampling_args: SamplingArgs,
+                      draft: modeling_drafter.DraftResult, verified) -> None:
+        llm = self.llm
+        fp, hidden, logits, smax, fused_head = verified
         B = st.kv_begin.shape[0]
         W, Lb = beam_shape.width, beam_shape.length
         code = _lib.dtype_code(llm.dtype)
@@ -158,52 +235,56 @@ class RecurrentDrafting(torch.nn.Module):
         cache_t = cache._cache
         NL, _, _, nkv, max_len, hd = cache_t.shape
         H = llm.config.hidden_size
-        with rec.time("generate_candidates"):
-            draft = drafter.beam_search_sparse(st.ctx, st.init_tok, llm.get_input_embeddings(), beam_shape)
-        with rec.time("verify_candidates"):
-            fp = tree_attention.pack_flat(draft.beams, st.kv_begin, st.kv_len, out=st.fp)
-            m_max = B * W * Lb
-            ws = llm.workspace(m_max, m_max)
-            with rec.time("base_forward"):
-                hidden = llm.backbone(ws, cache_t, m_max, fp.m_dev, fp.tokens, fp.tok_row, fp.tok_pos, fp.tok_slot,
-                                      fp.row_start, st.kv_begin, fp.base_len, B, W * Lb, s_max + W * Lb, _lib.ATTN_TREE,
-                                      tree_mask=fp.tree_mask, mask_words=fp.mask_words, n_pos=max_len + 1)
-                fused_head = llm.fused_head_ok()
-                smax = None
-                if sampling_args.greedy and fused_head:
-                    # the arg-max over the vocabulary rides on the LM head's epilogue: no logits are written
-                    llm.lm_argmax(hidden, st.llm_tok, m_dev=fp.m_dev)
-                    logits = ws["logits"]
-                elif sampling_args.greedy:
-                    logits = llm.lm_logits(hidden, ws["logits"], m_dev=fp.m_dev)
-                else:
-                    logits = ws["logits"]
-                    smax = llm.lm_logits_with_slice_max(hidden, logits, m_dev=fp.m_dev)
+        m_max = B * W * Lb
         V = logits.shape[1]
+        if sampling_args.greedy:
+            if not fused_head:
+                _lib.call("rd_argmax_rows", _lib.ptr(logits), logits.stride(0), m_max, _lib.ptr(fp.m_dev), V,
+                          _lib.ptr(st.llm_tok), None, sm)
+            _lib.call("rd_accept_commit_greedy", code, _lib.ptr(draft.beams), B, W, Lb, _lib.ptr(fp.unpacker),
+                      _lib.ptr(fp.row_start), _lib.ptr(st.llm_tok), _lib.ptr(hidden), H, _lib.ptr(cache_t), NL, nkv,
+                      max_len, hd, _lib.ptr(st.kv_begin), _lib.ptr(fp.base_len), _lib.ptr(st.kv_len),
+                      _lib.ptr(st.token_buf), _lib.ptr(st.n_accepted), _lib.ptr(st.seq_in_beam), _lib.ptr(st.init_tok),
+                      _lib.ptr(st.ctx), sm)
+        else:
+            modeling_drafter.vocab_topk(logits, st.p, subtract_max=False, temperature=sampling_args.temperature,
+                                        rows_dev=fp.m_dev, slice_max=smax)
+            u = torch.rand(B, W, Lb - 1, device=logits.device)
+            u_next = torch.rand(B, device=logits.device)
+            q = draft.q
+            _lib.call("rd_accept_commit_sample", code, _lib.ptr(draft.beams), B, W, Lb, V, _lib.ptr(fp.unpacker),
+                      _lib.ptr(fp.row_start), _lib.ptr(st.p.val), _lib.ptr(st.p.idx), _lib.ptr(st.p.cnt),
+                      _lib.ptr(st.p.masked), _lib.ptr_array([x.val for x in q]), _lib.ptr_array([x.idx for x in q]),
+                      _lib.ptr_array([x.cnt for x in q]), _lib.ptr_array([x.masked for x in q]), _lib.ptr(draft.anc),
+                      _lib.ptr(u), _lib.ptr(u_next), _lib.ptr(hidden), H, _lib.ptr(cache_t), NL, nkv, max_len, hd,
+                      _lib.ptr(st.kv_begin), _lib.ptr(fp.base_len), _lib.ptr(st.kv_len), _lib.ptr(st.token_buf),
+                      _lib.ptr(st.n_accepted), _lib.ptr(st.seq_in_beam), _lib.ptr(st.init_tok), _lib.ptr(st.ctx),
+                      None, sm)
+
+    def _step(self, st: _DecodeState, cache: kv_cache.Cache, beam_shape, sampling_args: SamplingArgs, s_max: int,
+              rec: stats.TextGeneration.Step, graphs: Optional["_StepGraphs"] = None) -> None:
+        """Enqueues one decode step.  No host synchronisation."""
+        if graphs is not None and graphs.ready:
+            with rec.time("generate_candidates"):
+                graphs.draft.replay()
+            with rec.time("verify_candidates"):
+                graphs.verify.replay()
+            with rec.time("accept_candidate_tokens"):
+                graphs.accept.replay()
+            _lib.count_replay(graphs.n_kernels)
+            return
+        with rec.time("generate_candidates"):
+            draft = self._draft_phase(st, beam_shape)
+        with rec.time("verify_candidates"):
+            verified = self._verify_phase(st, cache, beam_shape, sampling_args, draft, s_max, rec)
         with rec.time("accept_candidate_tokens"):
-            if sampling_args.greedy:
-                if not fused_head:
-                    _lib.call("rd_argmax_rows", _lib.ptr(logits), logits.stride(0), m_max, _lib.ptr(fp.m_dev), V,
-                              _lib.ptr(st.llm_tok), None, sm)
-                _lib.call("rd_accept_commit_greedy", code, _lib.ptr(draft.beams), B, W, Lb, _lib.ptr(fp.unpacker),
-                          _lib.ptr(fp.row_start), _lib.ptr(st.llm_tok), _lib.ptr(hidden), H, _lib.ptr(cache_t), NL, nkv,
-                          max_len, hd, _lib.ptr(st.kv_begin), _lib.ptr(fp.base_len), _lib.ptr(st.kv_len),
-                          _lib.ptr(st.token_buf), _lib.ptr(st.n_accepted), _lib.ptr(st.seq_in_beam), _lib.ptr(st.init_tok),
-                          _lib.ptr(st.ctx), sm)
-            else:
-                modeling_drafter.vocab_topk(logits, st.p, subtract_max=False, temperature=sampling_args.temperature,
-                                            rows_dev=fp.m_dev, slice_max=smax)
-                u = torch.rand(B, W, Lb - 1, device=logits.device)
-                u_next = torch.rand(B, device=logits.device)
-                q = draft.q
-                _lib.call("rd_accept_commit_sample", code, _lib.ptr(draft.beams), B, W, Lb, V, _lib.ptr(fp.unpacker),
-                          _lib.ptr(fp.row_start), _lib.ptr(st.p.val), _lib.ptr(st.p.idx), _lib.ptr(st.p.cnt),
-                          _lib.ptr(st.p.masked), _lib.ptr_array([x.val for x in q]), _lib.ptr_array([x.idx for x in q]),
-                          _lib.ptr_array([x.cnt for x in q]), _lib.ptr_array([x.masked for x in q]), _lib.ptr(draft.anc),
-                          _lib.ptr(u), _lib.ptr(u_next), _lib.ptr(hidden), H, _lib.ptr(cache_t), NL, nkv, max_len, hd,
-                          _lib.ptr(st.kv_begin), _lib.ptr(fp.base_len), _lib.ptr(st.kv_len), _lib.ptr(st.token_buf),
-                          _lib.ptr(st.n_accepted), _lib.ptr(st.seq_in_beam), _lib.ptr(st.init_tok), _lib.ptr(st.ctx),
-                          None, sm)
+            self._accept_phase(st, cache, beam_shape, sampling_args, draft, verified)
+
+    def _graphs_apply(self, sampling_args: SamplingArgs) -> bool:
+        """CUDA graphs are used for greedy decoding on the tensor-core path when enabled."""
+        llm = self.llm
+        return bool(self.cuda_graphs and sampling_args.greedy and llm.dtype == torch.bfloat16 and llm.head_dim == 128
+                    and llm.fused_head_ok())
 
     def _generate(self, text_generation: stats.TextGeneration, input_ids: torch.Tensor, max_length: int,
                   beam_shape: modeling_drafter.BeamShape, sampling_args: SamplingArgs,
@@ -232,9 +313,15 @@ class RecurrentDrafting(torch.nn.Module):
         assert max_length + Lb * W <= st.token_buf.shape[1] == cache._cache.shape[4]
         s_max = self._comprehend_prompt(st, cache, input_ids, sampling_args, special_tokens.pad)
         ref_len = seq_len  # the reference's padded sequence length S before the step
+        graphs = _StepGraphs() if self._graphs_apply(sampling_args) else None
+        n_steps = 0
         while seq_len < max_length:
+            if graphs is not None and not graphs.ready and n_steps == 2:
+                # replayed from this step on (the first two ran eagerly: every descriptor set and workspace exists)
+                graphs.capture(self, st, cache, beam_shape, sampling_args)
+            n_steps += 1
             with text_generation.step() as rec:
-                self._step(st, cache, beam_shape, sampling_args, s_max, rec)
+                self._step(st, cache, beam_shape, sampling_args, s_max, rec, graphs)
                 st.small_host.copy_(st.small, non_blocking=True)
                 torch.cuda.current_stream().synchronize()
                 if int(st.small_host[2, 0]) != 0:

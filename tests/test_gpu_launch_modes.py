@@ -35,7 +35,7 @@ def _child() -> None:
 
 def _run(env_extra):
     env = dict(os.environ)
-    for k in ("RD_PDL", "RD_FUSED_ROPE", "RD_GEMM_PAIRS", "RD_FUSED_HEAD"):
+    for k in ("RD_PDL", "RD_FUSED_ROPE", "RD_GEMM_PAIRS", "RD_FUSED_HEAD", "RD_CUDA_GRAPHS"):
         env.pop(k, None)
     env.update(env_extra)
     r = subprocess.run([sys.executable, os.path.abspath(__file__)], env=env, capture_output=True, text=True, timeout=600)
@@ -48,7 +48,8 @@ def _run(env_extra):
 def test_launch_and_fusion_switches_do_not_change_the_tokens():
     base = _run({})
     assert len(base) == 3 and all(len(row) == 96 for row in base)
-    for setting in ({"RD_PDL": "0"}, {"RD_FUSED_ROPE": "0"}, {"RD_GEMM_PAIRS": "0"}, {"RD_FUSED_HEAD": "0"}):
+    for setting in ({"RD_PDL": "0"}, {"RD_FUSED_ROPE": "0"}, {"RD_GEMM_PAIRS": "0"}, {"RD_FUSED_HEAD": "0"},
+                    {"RD_CUDA_GRAPHS": "0"}):
         assert _run(setting) == base, setting
 
 
