@@ -81,6 +81,16 @@ class _DecodeState:
         self.fp = tree_attention.alloc_flat(B, W, Lb, device)
         self.p = modeling_drafter.new_sparse(B * W * Lb, device)
         self.status = self.small[2, :1]
+        # the uniforms of a sampling step: one per drafted position and one for the token after the accepted prefix
+        self.u = torch.zeros(B, W, Lb - 1, dtype=torch.float32, device=device)
+        self.u_next = torch.zeros(B, dtype=torch.float32, device=device)
+
+    def draw_uniforms(self, B: int, W: int, Lb: int) -> None:
+        """Fills u and u_next from torch's generator, in this order (the order the reference draws them in)."""
+        for buf, shape in ((self.u, (B, W, Lb - 1)), (self.u_next, (B,))):
+            r = torch.rand(*shape, device=buf.device, out=buf)
+            if r is not buf:  # a stand-in for torch.rand that returns its own tensor
+                buf.copy_(r)
 
 
 class _StepGraphs:
@@ -122,7 +132,7 @@ class RecurrentDrafting(torch.nn.Module):
         super().__init__()
         self.llm = llm
         self.drafter = drafter
-        # replay each phase of a decode step from a CUDA graph (greedy, bf16, head_dim 128); the environment
+        # replay each phase of a decode step from a CUDA graph (bf16, head_dim 128); the environment
         # variable RD_CUDA_GRAPHS=0/1 sets the default
         self.cuda_graphs = (os.environ.get("RD_CUDA_GRAPHS", "1") != "0") if cuda_graphs is None else bool(cuda_graphs)
         self.last_state: Optional[_DecodeState] = None
@@ -249,8 +259,7 @@ class RecurrentDrafting(torch.nn.Module):
         else:
             modeling_drafter.vocab_topk(logits, st.p, subtract_max=False, temperature=sampling_args.temperature,
                                         rows_dev=fp.m_dev, slice_max=smax)
-            u = torch.rand(B, W, Lb - 1, device=logits.device)
-            u_next = torch.rand(B, device=logits.device)
+            u, u_next = st.u, st.u_next  # drawn by _step before this phase
             q = draft.q
             _lib.call("rd_accept_commit_sample", code, _lib.ptr(draft.beams), B, W, Lb, V, _lib.ptr(fp.unpacker),
                       _lib.ptr(fp.row_start), _lib.ptr(st.p.val), _lib.ptr(st.p.idx), _lib.ptr(st.p.cnt),
@@ -264,6 +273,8 @@ class RecurrentDrafting(torch.nn.Module):
     def _step(self, st: _DecodeState, cache: kv_cache.Cache, beam_shape, sampling_args: SamplingArgs, s_max: int,
               rec: stats.TextGeneration.Step, graphs: Optional["_StepGraphs"] = None) -> None:
         """Enqueues one decode step.  No host synchronisation."""
+        if not sampling_args.greedy:
+            st.draw_uniforms(st.kv_begin.shape[0], beam_shape.width, beam_shape.length)
         if graphs is not None and graphs.ready:
             with rec.time("generate_candidates"):
                 graphs.draft.replay()
@@ -281,10 +292,10 @@ class RecurrentDrafting(torch.nn.Module):
             self._accept_phase(st, cache, beam_shape, sampling_args, draft, verified)
 
     def _graphs_apply(self, sampling_args: SamplingArgs) -> bool:
-        """CUDA graphs are used for greedy decoding on the tensor-core path when enabled."""
+        """CUDA graphs are used on the tensor-core path when enabled (the uniforms of a sampling step are drawn
+        outside the graphs, from torch's generator as without them)."""
         llm = self.llm
-        return bool(self.cuda_graphs and sampling_args.greedy and llm.dtype == torch.bfloat16 and llm.head_dim == 128
-                    and llm.fused_head_ok())
+        return bool(self.cuda_graphs and llm.dtype == torch.bfloat16 and llm.head_dim == 128 and llm.fused_head_ok())
 
     def _generate(self, text_generation: stats.TextGeneration, input_ids: torch.Tensor, max_length: int,
                   beam_shape: modeling_drafter.BeamShape, sampling_args: SamplingArgs,

@@ -1,6 +1,7 @@
 """Replaying the phases of a decode step from CUDA graphs changes how the kernels are launched, not what they
 compute: the bf16 head_dim-128 model (tensor-core GEMMs, tcgen05 attention, fused heads) must yield the same
-token matrices, accepted counts and chosen beams step by step with and without graphs, left-padded rows included."""
+token matrices, accepted counts and chosen beams step by step with and without graphs, left-padded rows and a
+sampling run (same generator seed on both sides) included."""
 import numpy as np
 import pytest
 import torch
@@ -11,8 +12,8 @@ from gpu_helpers import HD128_DRAFTER, HD128_LLAMA, build_models, t
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("batch,width,length", [(4, 45, 5), (1, 8, 3)])
-def test_graph_replay_equals_eager_launches(batch, width, length):
+@pytest.mark.parametrize("batch,width,length,greedy", [(4, 45, 5, True), (1, 8, 3, True), (3, 15, 5, False)])
+def test_graph_replay_equals_eager_launches(batch, width, length, greedy):
     import recurrent_drafting as rd
 
     llm, dr, _, _ = build_models(HD128_LLAMA, HD128_DRAFTER, 77, dtype=torch.bfloat16)
@@ -21,9 +22,11 @@ def test_graph_replay_equals_eager_launches(batch, width, length):
     runs = []
     for graphs in (False, True):
         model = rd.RecurrentDrafting(llm, dr, cuda_graphs=graphs)
+        torch.manual_seed(99)  # a sampling run draws its uniforms from torch's generator, outside the graphs
+        sargs = rd.SamplingArgs(1.0, True) if greedy else rd.SamplingArgs(0.7, False)
         outs, acc, seqs = [], [], []
         launches0 = rd._lib.launches
-        for out in model.generate(rd.stats.Ledger(), prompt, 40 + 24, shape, rd.SamplingArgs(1.0, True), rd.SpecialTokens(0, None)):
+        for out in model.generate(rd.stats.Ledger(), prompt, 40 + 24, shape, sargs, rd.SpecialTokens(0, None)):
             st = model.last_state
             outs.append(out.cpu().numpy())
             acc.append(st.small_host[1].numpy().copy())
@@ -39,7 +42,7 @@ def test_graph_replay_equals_eager_launches(batch, width, length):
 
 
 def test_graphs_are_not_used_where_they_do_not_apply():
-    """fp32 models and sampling runs keep the ordinary launches even when graphs are requested."""
+    """fp32 models keep the ordinary launches even when graphs are requested."""
     import recurrent_drafting as rd
 
     llm, dr, _, _ = build_models(mb.NANO_LLAMA, mb.NANO_DRAFTER, 31)
@@ -47,4 +50,5 @@ def test_graphs_are_not_used_where_they_do_not_apply():
     assert not model._graphs_apply(rd.SamplingArgs(1.0, True))
     llm2, dr2, _, _ = build_models(HD128_LLAMA, HD128_DRAFTER, 77, dtype=torch.bfloat16)
     model2 = rd.RecurrentDrafting(llm2, dr2, cuda_graphs=True)
-    assert model2._graphs_apply(rd.SamplingArgs(1.0, True)) and not model2._graphs_apply(rd.SamplingArgs(0.8, False))
+    assert model2._graphs_apply(rd.SamplingArgs(1.0, True)) and model2._graphs_apply(rd.SamplingArgs(0.8, False))
+    assert not rd.RecurrentDrafting(llm2, dr2, cuda_graphs=False)._graphs_apply(rd.SamplingArgs(1.0, True))
