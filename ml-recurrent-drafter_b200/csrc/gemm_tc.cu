@@ -269,28 +269,44 @@ __device__ __forceinline__ void epilogue_math(float* v, const EpiArgs& e, int n,
   }
 }
 
-// Residual values of one token row: kOut consecutive output features starting at column n0.
+// How the lanes of an epilogue warp share the 32 tokens x kOut output features of a block when they read the
+// residual and write the result: every access is 16 bytes, the kLanes lanes of a group cover one token's
+// kOut features (64 contiguous bytes in bf16, 128 in fp32; half of that after SwiGLU), and the warp's groups
+// take kRows tokens per pass.  An instruction then touches kRows lines (4 to 16) instead of the 32 it would
+// with one token row per lane, which is what bounded the epilogue: the load/store unit handles one line of a
+// warp instruction at a time.
+template <bool OUT_F32, int kOut>
+struct EpiLanes {
+  static constexpr int kPer = OUT_F32 ? 4 : 8;   // output features per 16-byte access
+  static constexpr int kLanes = kOut / kPer;     // lanes per token row: 4 (bf16), 8 (fp32), 2 / 4 after SwiGLU
+  static constexpr int kRows = 32 / kLanes;      // token rows per pass
+  static constexpr int kPasses = kLanes;         // passes per 32-token block
+};
+
+// Residual values of a block in that arrangement: q[p] = the 16 bytes this lane adds in pass p.
 template <bool OUT_F32, int kOut>
 struct ResidualRegs {
-  uint4 q[OUT_F32 ? kOut / 4 : kOut / 8];
-  __device__ __forceinline__ void load(const EpiArgs& e, int tok, int n0, bool live) {
-    constexpr int nq = OUT_F32 ? kOut / 4 : kOut / 8;
-    if (live) {
-      const uint4* src = OUT_F32 ? reinterpret_cast<const uint4*>((const float*)e.R + (int64_t)tok * e.ldr + n0)
-                                 : reinterpret_cast<const uint4*>((const __nv_bfloat16*)e.R + (int64_t)tok * e.ldr + n0);
+  using G = EpiLanes<OUT_F32, kOut>;
+  uint4 q[G::kPasses];
+  __device__ __forceinline__ void load(const EpiArgs& e, int tok0, int n0, int tok_limit, int lane) {
+    const int sub = lane % G::kLanes, row0 = lane / G::kLanes;
+    constexpr int esz = OUT_F32 ? 4 : 2;
+    const char* base = (const char*)e.R + ((int64_t)(tok0 + row0) * e.ldr + n0 + sub * G::kPer) * esz;
 #pragma unroll
-      for (int j = 0; j < nq; ++j) q[j] = src[j];
-    }
+    for (int p = 0; p < G::kPasses; ++p)
+      if (tok0 + row0 + p * G::kRows < tok_limit)
+        q[p] = *reinterpret_cast<const uint4*>(base + (int64_t)p * G::kRows * e.ldr * esz);
   }
-  __device__ __forceinline__ void add_to(float* o) const {
+  __device__ __forceinline__ void add_to(int p, float* o) const {
     if (OUT_F32) {
-      const float* f = reinterpret_cast<const float*>(q);
-#pragma unroll
-      for (int j = 0; j < kOut; ++j) o[j] += f[j];
+      o[0] += __uint_as_float(q[p].x);
+      o[1] += __uint_as_float(q[p].y);
+      o[2] += __uint_as_float(q[p].z);
+      o[3] += __uint_as_float(q[p].w);
     } else {
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(q);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[p]);
 #pragma unroll
-      for (int j = 0; j < kOut / 2; ++j) {
+      for (int j = 0; j < 4; ++j) {
         const float2 f = __bfloat1622float2(h[j]);
         o[2 * j] += f.x;
         o[2 * j + 1] += f.y;
@@ -300,17 +316,17 @@ struct ResidualRegs {
 };
 
 // One 32-token block of a tile.  v: accumulator values in (lane = feature, i = token) layout after
-// epilogue_math.  The block is transposed through this warp's scratch so that each lane owns one
-// token and kOut consecutive output features, then written (and the residual read) with 16-byte
-// accesses.  `vec_ok` is false for ragged feature ranges or unaligned outputs: plain stores then.
+// epilogue_math.  The block is transposed through this warp's scratch (row = token) and read back in the
+// EpiLanes arrangement, so that the residual is read and the result written with 16-byte accesses that
+// cover whole token rows.  `vec_ok` is false for ragged feature ranges or unaligned outputs: plain stores then.
 template <int EPI, bool OUT_F32>
 __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float* scr, int lane, int n_warp0, int tok0,
                                                int tok_limit, int N, bool vec_ok,
                                                const ResidualRegs<OUT_F32, (EPI == RD_EPI_SWIGLU ? 16 : 32)>& res) {
   constexpr int kOut = (EPI == RD_EPI_SWIGLU) ? 16 : 32;  // output features per token of this warp
   constexpr bool kRes = (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES);
+  using G = EpiLanes<OUT_F32, kOut>;
   const int out0 = (EPI == RD_EPI_SWIGLU) ? (n_warp0 >> 1) : n_warp0;  // first output column of the warp
-  const int n_out_total = (EPI == RD_EPI_SWIGLU) ? (N >> 1) : N;
   if (!vec_ok) {
     // feature-per-lane fallback
     const int n = n_warp0 + lane;
@@ -338,58 +354,81 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
 #pragma unroll
   for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = v[i];
   __syncwarp();
-  float o[kOut];
+  const int sub = lane % G::kLanes, row0 = lane / G::kLanes;
+  float o[G::kPasses][G::kPer];
   if (EPI == RD_EPI_SWIGLU) {
-    // the token's 32 features are 16 (gate, up) pairs: one SiLU per output, no lane exchange
+    // the token's 32 features are 16 (gate, up) pairs: one SiLU per output, no lane exchange.  The SiLUs of the
+    // block are evaluated stage by stage (all exponentials, then all quotients) to keep the special-function
+    // unit's latency off the critical path.
+    float g[G::kPasses][G::kPer], u[G::kPasses][G::kPer];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float4 f = *reinterpret_cast<const float4*>(scr + lane * kScrLd + 4 * j);
-      o[2 * j] = rd::silu_f(f.x) * f.y;
-      o[2 * j + 1] = rd::silu_f(f.z) * f.w;
+    for (int p = 0; p < G::kPasses; ++p) {
+      const float* src = scr + (row0 + p * G::kRows) * kScrLd + sub * 2 * G::kPer;
+#pragma unroll
+      for (int j = 0; j < G::kPer / 2; ++j) {
+        const float4 f = *reinterpret_cast<const float4*>(src + 4 * j);
+        g[p][2 * j] = f.x;
+        u[p][2 * j] = f.y;
+        g[p][2 * j + 1] = f.z;
+        u[p][2 * j + 1] = f.w;
+      }
     }
+#pragma unroll
+    for (int p = 0; p < G::kPasses; ++p)
+#pragma unroll
+      for (int j = 0; j < G::kPer; ++j) o[p][j] = __expf(-g[p][j]);
+#pragma unroll
+    for (int p = 0; p < G::kPasses; ++p)
+#pragma unroll
+      for (int j = 0; j < G::kPer; ++j) o[p][j] = __fdividef(g[p][j], 1.0f + o[p][j]) * u[p][j];
   } else {
 #pragma unroll
-    for (int j = 0; j < kOut / 4; ++j) {
-      const float4 f = *reinterpret_cast<const float4*>(scr + lane * kScrLd + 4 * j);
-      o[4 * j] = f.x;
-      o[4 * j + 1] = f.y;
-      o[4 * j + 2] = f.z;
-      o[4 * j + 3] = f.w;
+    for (int p = 0; p < G::kPasses; ++p) {
+      const float* src = scr + (row0 + p * G::kRows) * kScrLd + sub * G::kPer;
+#pragma unroll
+      for (int j = 0; j < G::kPer / 4; ++j) {
+        const float4 f = *reinterpret_cast<const float4*>(src + 4 * j);
+        o[p][4 * j] = f.x;
+        o[p][4 * j + 1] = f.y;
+        o[p][4 * j + 2] = f.z;
+        o[p][4 * j + 3] = f.w;
+      }
     }
   }
   __syncwarp();  // the scratch is reused by the next block
-  const int tok = tok0 + lane;
-  if (tok < tok_limit) {
-    if (kRes) res.add_to(o);
-    float smax = -INFINITY;  // kEpiSliceMax: largest value of this token's 32 features AS STORED
-    if (OUT_F32) {
-      float4* dst = reinterpret_cast<float4*>((float*)e.C + (int64_t)tok * e.ldc + out0);
+  constexpr int esz = OUT_F32 ? 4 : 2;
+  char* dst0 = (char*)e.C + ((int64_t)(tok0 + row0) * e.ldc + out0 + sub * G::kPer) * esz;
 #pragma unroll
-      for (int j = 0; j < kOut / 4; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-      if (EPI == kEpiSliceMax) {
-#pragma unroll
-        for (int j = 0; j < kOut; ++j) smax = fmaxf(smax, o[j]);
-      }
-    } else {
-      uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)e.C + (int64_t)tok * e.ldc + out0);
-#pragma unroll
-      for (int j = 0; j < kOut / 8; ++j) {
-        uint4 pk;
+  for (int p = 0; p < G::kPasses; ++p) {
+    const int tok = tok0 + row0 + p * G::kRows;
+    const bool live = tok < tok_limit;
+    float smax = -INFINITY;  // kEpiSliceMax: largest value of the token's 32 features AS STORED
+    if (live) {
+      if (kRes) res.add_to(p, o[p]);
+      uint4 pk;
+      if (OUT_F32) {
+        pk = make_uint4(__float_as_uint(o[p][0]), __float_as_uint(o[p][1]), __float_as_uint(o[p][2]), __float_as_uint(o[p][3]));
+        if (EPI == kEpiSliceMax) smax = fmaxf(fmaxf(o[p][0], o[p][1]), fmaxf(o[p][2], o[p][3]));
+      } else {
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          h[t] = __floats2bfloat162_rn(o[8 * j + 2 * t], o[8 * j + 2 * t + 1]);
+          h[t] = __floats2bfloat162_rn(o[p][2 * t], o[p][2 * t + 1]);
           if (EPI == kEpiSliceMax) {
             const float2 r = __bfloat1622float2(h[t]);
             smax = fmaxf(smax, fmaxf(r.x, r.y));
           }
         }
-        dst[j] = pk;
       }
+      *reinterpret_cast<uint4*>(dst0 + (int64_t)p * G::kRows * e.ldc * esz) = pk;
     }
-    if (EPI == kEpiSliceMax) e.part_val[(int64_t)(n_warp0 >> 5) * e.part_ld + tok] = smax;
+    if (EPI == kEpiSliceMax) {
+      // the lanes of a group hold the pieces of one token row
+#pragma unroll
+      for (int d = 1; d < G::kLanes; d <<= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, d));
+      if (live && sub == 0) e.part_val[(int64_t)(n_warp0 >> 5) * e.part_ld + tok] = smax;
+    }
   }
-  (void)n_out_total;
 }
 
 // kEpiArgmax: one 32-token block of a tile.  v: accumulator values (lane = vocabulary id n_warp0 + lane,
@@ -652,7 +691,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t acc_phase = (local >> 1) & 1;
       // the first block's residual row is fetched while the main loop of this tile still runs
       ResidualRegs<OUT_F32, kOut> res_next;
-      if (kRes && vec_ok) res_next.load(epi, tok_base + lane, out0, tok_base + lane < tok_limit);
+      if (kRes && vec_ok) res_next.load(epi, tok_base, out0, tok_limit, lane);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
@@ -663,7 +702,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int c = 0; c < cols; c += 32) {
         ResidualRegs<OUT_F32, kOut> res_cur = res_next;
         if (kRes && vec_ok && c + 32 < cols)
-          res_next.load(epi, tok_base + c + 32 + lane, out0, tok_base + c + 32 + lane < tok_limit);
+          res_next.load(epi, tok_base + c + 32, out0, tok_limit, lane);
         uint32_t r[32];
         tmem_ld32(t_row + c, r);
         float v[32];
@@ -934,7 +973,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ResidualRegs<OUT_F32, kOut> res_next;
-      if (kRes && vec_ok) res_next.load(epi, tok_base + lane, out0, tok_base + lane < tok_limit);
+      if (kRes && vec_ok) res_next.load(epi, tok_base, out0, tok_limit, lane);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
@@ -945,7 +984,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int c = 0; c < cols; c += 32) {
         ResidualRegs<OUT_F32, kOut> res_cur = res_next;
         if (kRes && vec_ok && c + 32 < cols)
-          res_next.load(epi, tok_base + c + 32 + lane, out0, tok_base + c + 32 + lane < tok_limit);
+          res_next.load(epi, tok_base + c + 32, out0, tok_limit, lane);
         uint32_t r[32];
         tmem_ld32(t_row + c, r);
         float v[32];
