@@ -111,12 +111,14 @@ class _StepGraphs:
         stream.wait_stream(torch.cuda.current_stream())
         graphs = [torch.cuda.CUDAGraph() for _ in range(3)]
         before = _lib.launches
+        # thread-local capture mode: other threads of the process (a server's other requests) may keep calling CUDA
+        mode = dict(stream=stream, capture_error_mode="thread_local")
         with torch.cuda.stream(stream):
-            with torch.cuda.graph(graphs[0], stream=stream):
+            with torch.cuda.graph(graphs[0], **mode):
                 draft = model._draft_phase(st, beam_shape)
-            with torch.cuda.graph(graphs[1], stream=stream):
+            with torch.cuda.graph(graphs[1], **mode):
                 verified = model._verify_phase(st, cache, beam_shape, sampling_args, draft, 0)
-            with torch.cuda.graph(graphs[2], stream=stream):
+            with torch.cuda.graph(graphs[2], **mode):
                 model._accept_phase(st, cache, beam_shape, sampling_args, draft, verified)
         torch.cuda.current_stream().wait_stream(stream)
         # capturing enqueues nothing: the calls made above are the kernels of every later replay
