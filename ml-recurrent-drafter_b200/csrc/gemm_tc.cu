@@ -462,71 +462,105 @@ __device__ __forceinline__ void epilogue_argmax_block(const float* v, const EpiA
   }
 }
 
+__device__ __forceinline__ float4 ldg_f4(const float* p) {
+  float4 r;
+  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p));
+  return r;
+}
+
+// Per-token inputs of the rotary epilogue (the position, which leads to the cos/sin rows, and the row of the
+// token's slot in the cache), staged in shared memory for the whole tile by the four epilogue warps while the
+// tile's main loop still runs.  Fetched inside the block loop they cost ~1.5 k cycles per 32-token block even when
+// requested a block ahead: with global loads in flight, the waits for the shared-memory words of the
+// transposition waited for them too.
+constexpr int kRopeMetaBytes = 2 * kMaxChunk * 4;
+__device__ __forceinline__ void rope_meta_stage(const EpiArgs& e, int* s_pos, int* s_dst, int tok_base, int tok_limit, int et,
+                                                bool is_q, bool is_v) {
+#pragma unroll
+  for (int t = et; t < kMaxChunk; t += 128) {
+    const int tok = tok_base + t;
+    if (tok < tok_limit) {
+      if (!is_v) {
+        const int ps = e.tok_pos[tok];
+        s_pos[t] = ps < 0 ? 0 : (ps >= e.n_pos ? e.n_pos - 1 : ps);
+      }
+      // K and V heads: (row * nkv) * max_len + slot; kv head * max_len is added by the user
+      if (!is_q) s_dst[t] = e.tok_row[tok] * e.nkv * e.max_len + e.tok_slot[tok];
+    }
+  }
+}
+
 // Epilogue block of the QKV projection with fused rotary embedding (head_dim 128 = one CTA's 128
 // weight rows = one head).  v: this lane's feature d = 32*quarter + lane for the block's 32 tokens.
 // The rotation pairs feature d with d +- 64, which lives in the warp two quarters away, so the four
 // epilogue warps exchange their transposed blocks through the scratch and meet at a named barrier.
 // Values are rounded to bf16 first, as a separate projection would have stored them, so the result
-// equals projection -> rope bit for bit.
+// equals projection -> rope bit for bit.  After the exchange four lanes share a token row (8 features
+// each), so the cos/sin reads and the stores of an instruction cover 8 rows, not 32.
 __device__ __forceinline__ void epilogue_rope_block(const float* v, const EpiArgs& e, float* scr_all, int quarter, int lane,
-                                                    int head, int tok0, int tok_limit) {
+                                                    int head, int tok0, int tok_limit, const int* s_pos, const int* s_dst) {
   float* scr = scr_all + quarter * 32 * kScrLd;
+  const bool is_v = head >= e.nh + e.nkv;
+  const int sub = lane & 3, row0 = lane >> 2;
+  const int d0 = quarter * 32 + sub * 8;
+  const float sign = quarter < 2 ? -1.0f : 1.0f;  // rotate_half: (-x2, x1)
+  // the cos/sin rows of the block's tokens are requested first (volatile asm keeps them here): their latency
+  // runs under the transposition and the exchange below
+  float4 cs[4][4];
+  if (!is_v) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      if (tok0 + row0 + 8 * p < tok_limit) {
+        const int pos = s_pos[row0 + 8 * p];
+        const float* c = e.cos_t + (int64_t)pos * 128 + d0;
+        const float* sn = e.sin_t + (int64_t)pos * 128 + d0;
+        cs[p][0] = ldg_f4(c), cs[p][1] = ldg_f4(c + 4), cs[p][2] = ldg_f4(sn), cs[p][3] = ldg_f4(sn + 4);
+      }
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = __bfloat162float(__float2bfloat16_rn(v[i]));
   asm volatile("bar.sync 1, 128;" ::: "memory");
-  const bool is_v = head >= e.nh + e.nkv;
-  float o[32], p[32];
-  const float* own = scr + lane * kScrLd;
-  const float* oth = scr_all + (quarter ^ 2) * 32 * kScrLd + lane * kScrLd;
+  float o[4][8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float4 f = *reinterpret_cast<const float4*>(own + 4 * j);
-    o[4 * j] = f.x;
-    o[4 * j + 1] = f.y;
-    o[4 * j + 2] = f.z;
-    o[4 * j + 3] = f.w;
-    const float4 g = is_v ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(oth + 4 * j);
-    p[4 * j] = g.x;
-    p[4 * j + 1] = g.y;
-    p[4 * j + 2] = g.z;
-    p[4 * j + 3] = g.w;
-  }
-  asm volatile("bar.sync 1, 128;" ::: "memory");  // all four warps have read before the scratch is reused
-  const int tok = tok0 + lane;
-  if (tok >= tok_limit) return;
-  const int d0 = quarter * 32;
-  if (!is_v) {
-    int pos = e.tok_pos[tok];
-    pos = pos < 0 ? 0 : (pos >= e.n_pos ? e.n_pos - 1 : pos);
-    const float4* c4 = reinterpret_cast<const float4*>(e.cos_t + (int64_t)pos * 128 + d0);
-    const float4* s4 = reinterpret_cast<const float4*>(e.sin_t + (int64_t)pos * 128 + d0);
-    const float sign = quarter < 2 ? -1.0f : 1.0f;  // rotate_half: (-x2, x1)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float4 c = c4[j], sn = s4[j];
-      // two rounded products and one rounded sum, as the separate rope kernel computes them
-      o[4 * j] = __fadd_rn(__fmul_rn(o[4 * j], c.x), __fmul_rn(sign * p[4 * j], sn.x));
-      o[4 * j + 1] = __fadd_rn(__fmul_rn(o[4 * j + 1], c.y), __fmul_rn(sign * p[4 * j + 1], sn.y));
-      o[4 * j + 2] = __fadd_rn(__fmul_rn(o[4 * j + 2], c.z), __fmul_rn(sign * p[4 * j + 2], sn.z));
-      o[4 * j + 3] = __fadd_rn(__fmul_rn(o[4 * j + 3], c.w), __fmul_rn(sign * p[4 * j + 3], sn.w));
+  for (int p = 0; p < 4; ++p) {
+    const int r = row0 + 8 * p;
+    const float* own = scr + r * kScrLd + sub * 8;
+    const float4 a0 = *reinterpret_cast<const float4*>(own), a1 = *reinterpret_cast<const float4*>(own + 4);
+    o[p][0] = a0.x, o[p][1] = a0.y, o[p][2] = a0.z, o[p][3] = a0.w;
+    o[p][4] = a1.x, o[p][5] = a1.y, o[p][6] = a1.z, o[p][7] = a1.w;
+    if (!is_v) {
+      const float* oth = scr_all + (quarter ^ 2) * 32 * kScrLd + r * kScrLd + sub * 8;
+      const float4 b0 = *reinterpret_cast<const float4*>(oth), b1 = *reinterpret_cast<const float4*>(oth + 4);
+      if (tok0 + r < tok_limit) {
+        const float4 c0 = cs[p][0], c1 = cs[p][1], s0 = cs[p][2], s1 = cs[p][3];
+        // two rounded products and one rounded sum, as the separate rope kernel computes them
+        o[p][0] = __fadd_rn(__fmul_rn(o[p][0], c0.x), __fmul_rn(sign * b0.x, s0.x));
+        o[p][1] = __fadd_rn(__fmul_rn(o[p][1], c0.y), __fmul_rn(sign * b0.y, s0.y));
+        o[p][2] = __fadd_rn(__fmul_rn(o[p][2], c0.z), __fmul_rn(sign * b0.z, s0.z));
+        o[p][3] = __fadd_rn(__fmul_rn(o[p][3], c0.w), __fmul_rn(sign * b0.w, s0.w));
+        o[p][4] = __fadd_rn(__fmul_rn(o[p][4], c1.x), __fmul_rn(sign * b1.x, s1.x));
+        o[p][5] = __fadd_rn(__fmul_rn(o[p][5], c1.y), __fmul_rn(sign * b1.y, s1.y));
+        o[p][6] = __fadd_rn(__fmul_rn(o[p][6], c1.z), __fmul_rn(sign * b1.z, s1.z));
+        o[p][7] = __fadd_rn(__fmul_rn(o[p][7], c1.w), __fmul_rn(sign * b1.w, s1.w));
+      }
     }
   }
-  __nv_bfloat16* dst;
-  if (head < e.nh) {
-    dst = e.q_out + ((int64_t)tok * e.nh + head) * 128 + d0;
-  } else {
-    const int b = e.tok_row[tok], slot = e.tok_slot[tok];
-    const int kvh = is_v ? head - e.nh - e.nkv : head - e.nh;
-    dst = (is_v ? e.v_cache : e.k_cache) + (((int64_t)b * e.nkv + kvh) * e.max_len + slot) * 128 + d0;
-  }
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  asm volatile("bar.sync 1, 128;" ::: "memory");  // all four warps have read before the scratch is reused
+  const bool is_q = head < e.nh;
+  const int kvh = is_v ? head - e.nh - e.nkv : head - e.nh;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint4 pk;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+  for (int p = 0; p < 4; ++p) {
+    const int tok = tok0 + row0 + 8 * p;
+    if (tok < tok_limit) {
+      __nv_bfloat16* dst = is_q ? e.q_out + ((int64_t)tok * e.nh + head) * 128 + d0
+                                : (is_v ? e.v_cache : e.k_cache) + ((int64_t)s_dst[row0 + 8 * p] + (int64_t)kvh * e.max_len) * 128 + d0;
+      uint4 pk;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-    for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(o[8 * j + 2 * t], o[8 * j + 2 * t + 1]);
-    d4[j] = pk;
+      for (int t = 0; t < 4; ++t) h[t] = __floats2bfloat162_rn(o[p][2 * t], o[p][2 * t + 1]);
+      *reinterpret_cast<uint4*>(dst) = pk;
+    }
   }
 }
 
@@ -535,7 +569,8 @@ struct SmemLayout {
   static constexpr int kStageA = kMaxChunk * BK * 2;  // 32 KB: two 128-token boxes back to back
   static constexpr int kStages = 4;
   static constexpr int kScratch = 4 * 32 * kScrLd * 4;  // per-epilogue-warp transpose scratch
-  static constexpr int kBytes = kStages * (kStageW + kStageA) + kScratch + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kBytes =
+      kStages * (kStageW + kStageA) + kScratch + 1024 /*alignment slack*/ + 256 /*barriers*/ + kRopeMetaBytes;
 };
 
 template <int EPI, bool OUT_F32>
@@ -556,6 +591,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* acc_empty = acc_full + 2;       // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_pos = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);  // kEpiQkvRope: see rope_meta_stage
+  int* s_dst = s_pos + kMaxChunk;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   rd::pdl_launch_dependents();  // the next kernel may set itself up while this one runs
@@ -691,12 +728,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t acc_phase = (local >> 1) & 1;
       // the first block's residual row is fetched while the main loop of this tile still runs
       ResidualRegs<OUT_F32, kOut> res_next;
+      const int rope_head = (n_warp0 - quarter * 32) / 128;
+      if (EPI == kEpiQkvRope) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the blocks of the tile before have read their entries
+        rope_meta_stage(epi, s_pos, s_dst, tok_base, tok_limit, (int)threadIdx.x - 64, rope_head < epi.nh,
+                        rope_head >= epi.nh + epi.nkv);
+      }
       if (kRes && vec_ok) res_next.load(epi, tok_base, out0, tok_limit, lane);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      if (EPI == kEpiQkvRope) asm volatile("bar.sync 1, 128;" ::: "memory");  // the staged entries are visible
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
 #pragma unroll 1
       for (int c = 0; c < cols; c += 32) {
@@ -709,7 +753,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         if (EPI == kEpiQkvRope) {
-          epilogue_rope_block(v, epi, scratch, quarter, lane, (n_warp0 - quarter * 32) / 128, tok_base + c, tok_limit);
+          epilogue_rope_block(v, epi, scratch, quarter, lane, rope_head, tok_base + c, tok_limit, s_pos + c, s_dst + c);
         } else if (EPI == kEpiArgmax) {
           epilogue_argmax_block(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N);
         } else {
@@ -802,7 +846,7 @@ struct SmemLayoutPair {
   static constexpr int kStageA = kSub * kBoxA;
   static constexpr int kStages = 6;
   static constexpr int kScratch = 4 * 32 * kScrLd * 4;
-  static constexpr int kBytes = kStages * (kStageW + kStageA) + kScratch + 1024 + 256;
+  static constexpr int kBytes = kStages * (kStageW + kStageA) + kScratch + 1024 + 256 + kRopeMetaBytes;
 };
 
 template <int EPI, bool OUT_F32>
@@ -823,6 +867,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* acc_empty = acc_full + 2;       // [2] used in the leader CTA (8 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_pos = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);  // kEpiQkvRope: see rope_meta_stage
+  int* s_dst = s_pos + kMaxChunk;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
@@ -973,12 +1019,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ResidualRegs<OUT_F32, kOut> res_next;
+      const int rope_head = (n_warp0 - quarter * 32) / 128;
+      if (EPI == kEpiQkvRope) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the blocks of the tile before have read their entries
+        rope_meta_stage(epi, s_pos, s_dst, tok_base, tok_limit, (int)threadIdx.x - 64, rope_head < epi.nh,
+                        rope_head >= epi.nh + epi.nkv);
+      }
       if (kRes && vec_ok) res_next.load(epi, tok_base, out0, tok_limit, lane);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      if (EPI == kEpiQkvRope) asm volatile("bar.sync 1, 128;" ::: "memory");  // the staged entries are visible
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
 #pragma unroll 1
       for (int c = 0; c < cols; c += 32) {
@@ -991,7 +1044,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         if (EPI == kEpiQkvRope) {
-          epilogue_rope_block(v, epi, scratch, quarter, lane, (n_warp0 - quarter * 32) / 128, tok_base + c, tok_limit);
+          epilogue_rope_block(v, epi, scratch, quarter, lane, rope_head, tok_base + c, tok_limit, s_pos + c, s_dst + c);
         } else if (EPI == kEpiArgmax) {
           epilogue_argmax_block(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N);
         } else {
