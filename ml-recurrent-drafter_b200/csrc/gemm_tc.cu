@@ -297,6 +297,29 @@ struct ResidualRegs {
       if (tok0 + row0 + p * G::kRows < tok_limit)
         q[p] = *reinterpret_cast<const uint4*>(base + (int64_t)p * G::kRows * e.ldr * esz);
   }
+  // bf16 residual through shared memory: request() starts asynchronous copies of the block's 16-byte pieces into
+  // this warp's staging buffer (every lane copies the pieces it will add itself: slot p * 32 + lane), take() waits for
+  // them and moves them to registers.  Unlike register loads the copies are not tracked by the load scoreboards, so
+  // the waits for the shared-memory words of the transposition do not wait for them: with the next block's
+  // residual in flight as ordinary loads each block paid most of an L2 latency.  `after`: a register the copies are
+  // issued after (the last word taken from the buffer they overwrite).
+  __device__ __forceinline__ void request(const EpiArgs& e, int tok0, int n0, int tok_limit, int lane, uint4* buf,
+                                          uint32_t after) const {
+    const int sub = lane % G::kLanes, row0 = lane / G::kLanes;
+    const __nv_bfloat16* base = (const __nv_bfloat16*)e.R + (int64_t)(tok0 + row0) * e.ldr + n0 + sub * G::kPer;
+#pragma unroll
+    for (int p = 0; p < G::kPasses; ++p)
+      if (tok0 + row0 + p * G::kRows < tok_limit)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(buf + p * 32 + lane)),
+                     "l"(base + (int64_t)p * G::kRows * e.ldr), "r"(after)
+                     : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  __device__ __forceinline__ void take(const uint4* buf, int lane) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int p = 0; p < G::kPasses; ++p) q[p] = buf[p * 32 + lane];
+  }
   __device__ __forceinline__ void add_to(int p, float* o) const {
     if (OUT_F32) {
       o[0] += __uint_as_float(q[p].x);
@@ -474,6 +497,8 @@ __device__ __forceinline__ float4 ldg_f4(const float* p) {
 // requested a block ahead: with global loads in flight, the waits for the shared-memory words of the
 // transposition waited for them too.
 constexpr int kRopeMetaBytes = 2 * kMaxChunk * 4;
+constexpr int kEpiStageBytes = 4 * 128 * 16;  // the larger of the two uses of the epilogue staging area
+static_assert(kEpiStageBytes >= kRopeMetaBytes, "staging area");
 __device__ __forceinline__ void rope_meta_stage(const EpiArgs& e, int* s_pos, int* s_dst, int tok_base, int tok_limit, int et,
                                                 bool is_q, bool is_v) {
 #pragma unroll
@@ -570,7 +595,7 @@ struct SmemLayout {
   static constexpr int kStages = 4;
   static constexpr int kScratch = 4 * 32 * kScrLd * 4;  // per-epilogue-warp transpose scratch
   static constexpr int kBytes =
-      kStages * (kStageW + kStageA) + kScratch + 1024 /*alignment slack*/ + 256 /*barriers*/ + kRopeMetaBytes;
+      kStages * (kStageW + kStageA) + kScratch + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiStageBytes;
 };
 
 template <int EPI, bool OUT_F32>
@@ -591,8 +616,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* acc_empty = acc_full + 2;       // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* s_pos = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);  // kEpiQkvRope: see rope_meta_stage
+  // staging area of the epilogue warps: rope_meta_stage (kEpiQkvRope) or the residual pieces (ResidualRegs::request)
+  int* s_pos = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);
   int* s_dst = s_pos + kMaxChunk;
+  uint4* res_buf = reinterpret_cast<uint4*>(s_pos) + ((threadIdx.x >> 5) & 3) * 128;  // 2 KB per epilogue warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   rd::pdl_launch_dependents();  // the next kernel may set itself up while this one runs
@@ -734,7 +761,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         rope_meta_stage(epi, s_pos, s_dst, tok_base, tok_limit, (int)threadIdx.x - 64, rope_head < epi.nh,
                         rope_head >= epi.nh + epi.nkv);
       }
-      if (kRes && vec_ok) res_next.load(epi, tok_base, out0, tok_limit, lane);
+      if (kRes && vec_ok) {
+        if (OUT_F32)
+          res_next.load(epi, tok_base, out0, tok_limit, lane);
+        else
+          res_next.request(epi, tok_base, out0, tok_limit, lane, res_buf, 0u);
+      }
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
@@ -744,9 +776,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
 #pragma unroll 1
       for (int c = 0; c < cols; c += 32) {
+        if (kRes && vec_ok && !OUT_F32) res_next.take(res_buf, lane);
         ResidualRegs<OUT_F32, kOut> res_cur = res_next;
-        if (kRes && vec_ok && c + 32 < cols)
-          res_next.load(epi, tok_base + c + 32, out0, tok_limit, lane);
+        if (kRes && vec_ok && c + 32 < cols) {
+          if (OUT_F32)
+            res_next.load(epi, tok_base + c + 32, out0, tok_limit, lane);
+          else
+            res_next.request(epi, tok_base + c + 32, out0, tok_limit, lane, res_buf, res_cur.q[EpiLanes<OUT_F32, kOut>::kPasses - 1].w);
+        }
         uint32_t r[32];
         tmem_ld32(t_row + c, r);
         float v[32];
@@ -846,7 +883,7 @@ struct SmemLayoutPair {
   static constexpr int kStageA = kSub * kBoxA;
   static constexpr int kStages = 6;
   static constexpr int kScratch = 4 * 32 * kScrLd * 4;
-  static constexpr int kBytes = kStages * (kStageW + kStageA) + kScratch + 1024 + 256 + kRopeMetaBytes;
+  static constexpr int kBytes = kStages * (kStageW + kStageA) + kScratch + 1024 + 256 + kEpiStageBytes;
 };
 
 template <int EPI, bool OUT_F32>
@@ -867,8 +904,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* acc_empty = acc_full + 2;       // [2] used in the leader CTA (8 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* s_pos = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);  // kEpiQkvRope: see rope_meta_stage
+  // staging area of the epilogue warps: rope_meta_stage (kEpiQkvRope) or the residual pieces (ResidualRegs::request)
+  int* s_pos = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);
   int* s_dst = s_pos + kMaxChunk;
+  uint4* res_buf = reinterpret_cast<uint4*>(s_pos) + ((threadIdx.x >> 5) & 3) * 128;  // 2 KB per epilogue warp
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
@@ -1025,7 +1064,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         rope_meta_stage(epi, s_pos, s_dst, tok_base, tok_limit, (int)threadIdx.x - 64, rope_head < epi.nh,
                         rope_head >= epi.nh + epi.nkv);
       }
-      if (kRes && vec_ok) res_next.load(epi, tok_base, out0, tok_limit, lane);
+      if (kRes && vec_ok) {
+        if (OUT_F32)
+          res_next.load(epi, tok_base, out0, tok_limit, lane);
+        else
+          res_next.request(epi, tok_base, out0, tok_limit, lane, res_buf, 0u);
+      }
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
@@ -1035,9 +1079,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
 #pragma unroll 1
       for (int c = 0; c < cols; c += 32) {
+        if (kRes && vec_ok && !OUT_F32) res_next.take(res_buf, lane);
         ResidualRegs<OUT_F32, kOut> res_cur = res_next;
-        if (kRes && vec_ok && c + 32 < cols)
-          res_next.load(epi, tok_base + c + 32, out0, tok_limit, lane);
+        if (kRes && vec_ok && c + 32 < cols) {
+          if (OUT_F32)
+            res_next.load(epi, tok_base + c + 32, out0, tok_limit, lane);
+          else
+            res_next.request(epi, tok_base + c + 32, out0, tok_limit, lane, res_buf, res_cur.q[EpiLanes<OUT_F32, kOut>::kPasses - 1].w);
+        }
         uint32_t r[32];
         tmem_ld32(t_row + c, r);
         float v[32];
