@@ -39,6 +39,7 @@ namespace {
 
 constexpr int BM = 128;       // weight rows per tile (MMA M)
 constexpr int kMaxChunk = 256;  // tokens per tile (MMA N), multiple of 16
+constexpr int kTokBox = 32;     // token rows per TMA box of the pair kernel
 constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
@@ -69,8 +70,14 @@ __device__ unsigned long long* g_gemm_timing = nullptr;
 #define RD_TIMING_END(M, N, K) do { } while (0)
 #endif
 
+// Token-operand descriptors of the pair kernel, one per box height (multiples of kTokBox rows up to a CTA's 128).
+struct TokMaps {
+  CUtensorMap m[4];
+};
+
 struct GemmPlan {
-  CUtensorMap map_a;  // activations [m_max, K], box 64 x 128
+  CUtensorMap map_a;    // activations [m_max, K], box 64 x 128 (single-CTA kernel)
+  TokMaps maps_a;       // the same tensor in boxes of 64 x 32/64/96/128: the pair kernel fetches only the rows its chunk fills
   CUtensorMap map_w;  // weights [N, K], box 64 x 128
   int m_max, N, K;
 };
@@ -248,9 +255,8 @@ constexpr int kScrLd = 36;  // floats per scratch row: 16-byte aligned rows, con
 
 // Element-wise part of the epilogue in accumulator layout (lane = output feature n, i = token).
 template <int EPI>
-__device__ __forceinline__ void epilogue_math(float* v, const EpiArgs& e, int n, int N, bool swiglu_here) {
+__device__ __forceinline__ void epilogue_math(float* v, const EpiArgs& e, int n, int N, bool swiglu_here, float bias) {
   if (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES) {
-    const float bias = n < N ? __bfloat162float(e.bias[n]) : 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] += bias;
   }
@@ -755,6 +761,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t acc_phase = (local >> 1) & 1;
       // the first block's residual row is fetched while the main loop of this tile still runs
       ResidualRegs<OUT_F32, kOut> res_next;
+      // this lane's bias, read once per tile and ahead of the wait (a load inside the block loop stalls every block)
+      constexpr bool kBias = (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES);
+      const float bias = (kBias && n_warp0 + lane < N) ? __bfloat162float(epi.bias[n_warp0 + lane]) : 0.f;
       const int rope_head = (n_warp0 - quarter * 32) / 128;
       if (EPI == kEpiQkvRope) {
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the blocks of the tile before have read their entries
@@ -794,7 +803,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         } else if (EPI == kEpiArgmax) {
           epilogue_argmax_block(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N);
         } else {
-          epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok);
+          epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok, bias);
           epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
         }
       }
@@ -875,10 +884,11 @@ __device__ __forceinline__ uint32_t umma_instr_desc_pair(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
+constexpr int kTokBoxBytes = kTokBox * BK * 2;  // 4 KB
 struct SmemLayoutPair {
   static constexpr int kSub = 1;                       // k-blocks of 64 per pipeline stage (2 with 3 stages measured the same)
   static constexpr int kBoxW = BM * BK * 2;            // 16 KB: this CTA's 128 weight rows of one k-block
-  static constexpr int kBoxA = 128 * BK * 2;           // 16 KB: this CTA's half of the token tile of one k-block
+  static constexpr int kBoxA = 128 * BK * 2;           // 16 KB: this CTA's half of the token tile of one k-block (up to 4 boxes)
   static constexpr int kStageW = kSub * kBoxW;
   static constexpr int kStageA = kSub * kBoxA;
   static constexpr int kStages = 6;
@@ -888,7 +898,7 @@ struct SmemLayoutPair {
 
 template <int EPI, bool OUT_F32>
 __global__ void __launch_bounds__(kThreads, 1)
-    gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, EpiArgs epi,
+    gemm_tc_pair_kernel(const __grid_constant__ TokMaps maps_a, const __grid_constant__ CUtensorMap map_w, EpiArgs epi,
                         int m_max, const int32_t* __restrict__ m_dev, int N, int K, int32_t* status) {
   using L = SmemLayoutPair;
   constexpr int kStages = L::kStages;
@@ -915,7 +925,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   rd::pdl_launch_dependents();  // the next kernel may set itself up while this one runs
   if (threadIdx.x == 0) {
     // the descriptors are kernel parameters: their fetch may start before the dependency wait
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    for (int i = 0; i < 4; ++i) asm volatile("prefetch.tensormap [%0];" ::"l"(&maps_a.m[i]) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
   }
 
@@ -969,6 +979,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int w_pair = tile / ch.n_chunks, ci = tile % ch.n_chunks;
         const int cols = chunk_cols(ch, ci, M);
         const int tok0 = ci * ch.chunk + (int)rank * (cols >> 1);  // this CTA's half of the chunk
+        const int n_box = ((cols >> 1) + kTokBox - 1) / kTokBox;
+        const CUtensorMap* map_a = &maps_a.m[n_box - 1];
         const int w_row0 = w_pair * 2 * BM + (int)rank * BM;
         for (int kb = 0; kb < k_blocks; kb += L::kSub) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
@@ -977,10 +989,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           const int n_sub = min(L::kSub, k_blocks - kb);
           const uint32_t leader_full = mapa_u32(smem_u32(&full[stage]), 0);
-          if (rank == 0) mbar_expect_tx(&full[stage], 2 * n_sub * (L::kBoxW + L::kBoxA));
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * n_sub * (L::kBoxW + n_box * kTokBoxBytes));
           for (int sb = 0; sb < n_sub; ++sb) {
             tma_load_2d_pair(sW + stage * L::kStageW + sb * L::kBoxW, &map_w, leader_full, (kb + sb) * BK, w_row0);
-            tma_load_2d_pair(sA + stage * L::kStageA + sb * L::kBoxA, &map_a, leader_full, (kb + sb) * BK, tok0);
+            // one box of just the rows the chunk's half fills (rounded up to 32): a chunk of 192 tokens moves 96
+            // rows per CTA, not 128, and the main loop is bound by these bytes.  (Several 32-row boxes instead of
+            // one tall one made the loop 25 % slower: the cost is per box as well as per byte.)
+            tma_load_2d_pair(sA + stage * L::kStageA + sb * L::kBoxA, map_a, leader_full, (kb + sb) * BK, tok0);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -1058,6 +1073,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ResidualRegs<OUT_F32, kOut> res_next;
+      // this lane's bias, read once per tile and ahead of the wait (a load inside the block loop stalls every block)
+      constexpr bool kBias = (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES);
+      const float bias = (kBias && n_warp0 + lane < N) ? __bfloat162float(epi.bias[n_warp0 + lane]) : 0.f;
       const int rope_head = (n_warp0 - quarter * 32) / 128;
       if (EPI == kEpiQkvRope) {
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the blocks of the tile before have read their entries
@@ -1097,7 +1115,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         } else if (EPI == kEpiArgmax) {
           epilogue_argmax_block(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N);
         } else {
-          epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok);
+          epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok, bias);
           epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
         }
       }
@@ -1195,7 +1213,7 @@ int launch_cluster2(Kern kern, int grid, int smem_bytes, cudaStream_t s, const G
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (n_configured < 64) configured[n_configured++] = (const void*)kern;
   }
-  cudaError_t err = rd::launch_chained(kern, dim3(grid), dim3(kThreads), smem_bytes, s, 2, p->map_a, p->map_w, e, p->m_max, m_dev,
+  cudaError_t err = rd::launch_chained(kern, dim3(grid), dim3(kThreads), smem_bytes, s, 2, p->maps_a, p->map_w, e, p->m_max, m_dev,
                                        p->N, p->K, status);
   RD_CHECK_CHAINED(err);
   return RD_OK;
@@ -1279,7 +1297,9 @@ extern "C" void* rd_gemm_plan_create(const void* A, int64_t lda, int m_max, cons
   p->m_max = m_max;
   p->N = N;
   p->K = K;
-  if (!make_map(&p->map_a, A, lda, m_max, K, 128) || !make_map(&p->map_w, W, ldw, N, K, BM)) {
+  bool ok = make_map(&p->map_a, A, lda, m_max, K, 128) && make_map(&p->map_w, W, ldw, N, K, BM);
+  for (int i = 0; ok && i < 4; ++i) ok = make_map(&p->maps_a.m[i], A, lda, m_max, K, (i + 1) * kTokBox);
+  if (!ok) {
     delete p;
     return nullptr;
   }
