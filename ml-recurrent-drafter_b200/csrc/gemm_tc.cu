@@ -10,8 +10,9 @@
 // features): a persistent kernel, one CTA per SM, CTAs paired in clusters of two that share one
 // tcgen05.mma.cta_group::2 of 256 weight rows x (up to 256) tokens x 16:
 //   warp 0     TMA producer in BOTH CTAs: cp.async.bulk.tensor loads (128-byte swizzle, never
-//              multicast) of this CTA's 128 weight rows and of its HALF of the token tile, six
-//              stages of 32 KB; both CTAs' loads complete on the leader's mbarrier;
+//              multicast) of this CTA's 128 weight rows and of its HALF of the token tile (one box
+//              of 32/64/96/128 rows, whichever the chunk's half fills), six stages of 32 KB; both
+//              CTAs' loads complete on the leader's mbarrier;
 //   warp 1     MMA issuer, leader CTA only: one elected thread issues the MMAs for the pair into
 //              one of two TMEM accumulator buffers (each CTA's TMEM receives its 128 rows) and
 //              frees a stage / publishes an accumulator with ONE tcgen05.commit whose arrival is
@@ -19,9 +20,13 @@
 //   warps 2-5  epilogue in both CTAs: tcgen05.ld of the accumulator (each warp its own 32 TMEM
 //              lanes), the fused element-wise part (bias / SiLU / SwiGLU / residual / rotary
 //              embedding + cache append / arg-max or slice maxima over the vocabulary), a transpose
-//              through shared memory to one token per lane and 16-byte global stores, overlapped
-//              with the next tile's main loop through the second accumulator buffer; the peer's
-//              epilogue frees the accumulator with remote mbarrier arrives.
+//              through shared memory after which groups of lanes share token rows, so that every
+//              16-byte residual read and store instruction covers whole rows; inputs of the block
+//              loop that come from global memory (residual, rotary positions, bias) are staged
+//              ahead of it (cp.async or shared memory): a global load in flight makes the waits for
+//              the transposition's shared-memory words wait for it as well.  Overlapped with the next
+//              tile's main loop through the second accumulator buffer; the peer's epilogue frees the
+//              accumulator with remote mbarrier arrives.
 // gemm_tc_kernel is the single-CTA form of the same design (cta_group::1, 128 weight rows per tile,
 // four stages) for matrices with fewer than 256 output features.
 // Tiles are walked weight-tile-major so that the CTAs running at the same time share W tiles
@@ -39,7 +44,7 @@ namespace {
 
 constexpr int BM = 128;       // weight rows per tile (MMA M)
 constexpr int kMaxChunk = 256;  // tokens per tile (MMA N), multiple of 16
-constexpr int kTokBox = 32;     // token rows per TMA box of the pair kernel
+constexpr int kTokBox = 32;     // granularity of the pair kernel's token boxes (rows)
 constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
