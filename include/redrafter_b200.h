@@ -186,6 +186,28 @@ RD_API int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, void
                              const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv, int hd,
                              int max_len, int32_t* status, void* stream);
 
+/* LlamaRMSNorm (modeling_llama.py:21-34) folded into the two GEMMs around it, so that the norm between a residual
+ * projection and the next projection needs no kernel of its own (bf16, tensor-core path).
+ * rd_gemm_bf16_tc_res_norm (producer): C = A W^T + R as RD_EPI_RES; besides, C2[t, n] = bf16(C[t, n]) * gamma[n] and
+ * ss_out[t * ss_ld + n / 128] = the sum over the 128 features of slice n / 128 of bf16(C[t, n])^2 (fp32, every slice
+ * of every live token is written: nothing to zero, no atomics, the same bits from launch to launch).  N a multiple
+ * of 128, ss_ld >= N / 128 and a multiple of 4 with a 16-byte aligned base for the consumers, 16-byte aligned rows.
+ * rd_gemm_bf16_tc_swiglu_normed / rd_gemm_bf16_tc_qkv_rope_normed (consumers): as RD_EPI_SWIGLU /
+ * rd_gemm_bf16_tc_qkv_rope on an A that is such a C2; the accumulator row of token t is multiplied by
+ * 1 / sqrt(sum_{s < ss_slices} ss_in[t * ss_ld + s] / norm_dim + eps) first (slices added in ascending order).
+ * Against the separate rd_rmsnorm the row is rounded once (x * gamma) instead of twice (x / rms, then * gamma) before
+ * the projection, and scaled in fp32 afterwards: results agree within bf16 rounding, not bit for bit. */
+RD_API int rd_gemm_bf16_tc_res_norm(const void* plan, void* C, int64_t ldc, const void* R, int64_t ldr, const int32_t* m_dev,
+                             const void* gamma, void* C2, int64_t ldc2, float* ss_out, int64_t ss_ld, int32_t* status,
+                             void* stream);
+RD_API int rd_gemm_bf16_tc_swiglu_normed(const void* plan, void* C, int64_t ldc, const int32_t* m_dev, const float* ss_in,
+                                  int64_t ss_ld, int ss_slices, int norm_dim, float eps, int32_t* status, void* stream);
+RD_API int rd_gemm_bf16_tc_qkv_rope_normed(const void* plan, const int32_t* m_dev, void* q_out, void* k_cache, void* v_cache,
+                                    const int32_t* tok_row, const int32_t* tok_pos, const int32_t* tok_slot,
+                                    const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv, int hd,
+                                    int max_len, const float* ss_in, int64_t ss_ld, int ss_slices, int norm_dim, float eps,
+                                    int32_t* status, void* stream);
+
 /* The LM head of the greedy verify step with the arg-max over the vocabulary done in its epilogue
  * (modeling_llama.py:272 followed by recurrent_drafting.py:52): `plan` holds (final hidden states,
  * lm_head weight [V, H]); the fp32 logits are never written.  Every 32 consecutive vocabulary ids of a

@@ -242,6 +242,22 @@ struct EpiArgs {
   const float* cos_t;
   const float* sin_t;
   int n_pos, nh, nkv, max_len;
+  // LlamaRMSNorm folded into the two GEMMs around it (optional; bf16 output, N a multiple of 32).
+  // Producer (residual epilogues, gamma != nullptr): besides C the kernel writes C2 = bf16(C) * gamma and, per token
+  // and 128-feature slice (a CTA's rows), the sum of squares of the rounded C values to
+  // ss_out[token * ss_out_ld + slice]: no atomics, so the statistics are the same bits from launch to launch.
+  // Consumer (SwiGLU and QKV-rope epilogues, ss_in != nullptr): the A rows are such a C2 (scaled by gamma, not
+  // normalised); the accumulator row of token t is multiplied by 1 / sqrt(sum_slices ss_in[t][slice] / norm_dim + eps),
+  // the slices added in ascending order, before the rest of the epilogue.
+  const __nv_bfloat16* gamma;
+  __nv_bfloat16* C2;
+  int64_t ldc2;
+  float* ss_out;
+  int64_t ss_out_ld;
+  const float* ss_in;
+  int64_t ss_in_ld;
+  int ss_slices;
+  float norm_dim, norm_eps;
   // kEpiArgmax / kEpiSliceMax only: per (32-feature slice, token) partial results, laid out [slice][part_ld]
   float* part_val;               // kEpiSliceMax: largest stored value
   unsigned long long* part_key;  // kEpiArgmax: (order-preserving key of the largest logit) << 32 | ~(first id holding it)
@@ -356,7 +372,8 @@ struct ResidualRegs {
 template <int EPI, bool OUT_F32>
 __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float* scr, int lane, int n_warp0, int tok0,
                                                int tok_limit, int N, bool vec_ok,
-                                               const ResidualRegs<OUT_F32, (EPI == RD_EPI_SWIGLU ? 16 : 32)>& res) {
+                                               const ResidualRegs<OUT_F32, (EPI == RD_EPI_SWIGLU ? 16 : 32)>& res,
+                                               const float* s_scale, uint4 gamma8, float* ss_red_block) {
   constexpr int kOut = (EPI == RD_EPI_SWIGLU) ? 16 : 32;  // output features per token of this warp
   constexpr bool kRes = (EPI == RD_EPI_BIAS_SILU_RES || EPI == RD_EPI_RES);
   using G = EpiLanes<OUT_F32, kOut>;
@@ -389,6 +406,7 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
   for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = v[i];
   __syncwarp();
   const int sub = lane % G::kLanes, row0 = lane / G::kLanes;
+  float* const ss_red = ss_red_block + ((n_warp0 >> 5) & 3) * 32;  // this warp's row of the reduction buffer
   float o[G::kPasses][G::kPer];
   if (EPI == RD_EPI_SWIGLU) {
     // the token's 32 features are 16 (gate, up) pairs: one SiLU per output, no lane exchange.  The SiLUs of the
@@ -405,6 +423,15 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
         u[p][2 * j] = f.y;
         g[p][2 * j + 1] = f.z;
         u[p][2 * j + 1] = f.w;
+      }
+    }
+    if (s_scale != nullptr) {
+      // folded RMS norm: gate and up of a token are scaled by the token's 1 / rms first
+#pragma unroll
+      for (int p = 0; p < G::kPasses; ++p) {
+        const float sc = s_scale[row0 + p * G::kRows];
+#pragma unroll
+        for (int j = 0; j < G::kPer; ++j) g[p][j] *= sc, u[p][j] *= sc;
       }
     }
 #pragma unroll
@@ -437,6 +464,7 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
     const int tok = tok0 + row0 + p * G::kRows;
     const bool live = tok < tok_limit;
     float smax = -INFINITY;  // kEpiSliceMax: largest value of the token's 32 features AS STORED
+    float ss_part = 0.f;     // folded RMS norm: this lane's share of the token's sum of squares
     if (live) {
       if (kRes) res.add_to(p, o[p]);
       uint4 pk;
@@ -455,12 +483,45 @@ __device__ __forceinline__ void epilogue_block(float* v, const EpiArgs& e, float
         }
       }
       *reinterpret_cast<uint4*>(dst0 + (int64_t)p * G::kRows * e.ldc * esz) = pk;
+      if (kRes && !OUT_F32 && e.gamma != nullptr) {
+        // producer side of the folded RMS norm: statistics and the next GEMM's operand come from the ROUNDED row
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gamma8);
+        uint4 pk2;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk2);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = __bfloat1622float2(h[t]);
+          const float2 gm = __bfloat1622float2(g2[t]);
+          ss_part += f.x * f.x + f.y * f.y;
+          h2[t] = __floats2bfloat162_rn(f.x * gm.x, f.y * gm.y);
+        }
+        *reinterpret_cast<uint4*>(e.C2 + (int64_t)tok * e.ldc2 + out0 + sub * G::kPer) = pk2;
+      }
+    }
+    if (kRes && !OUT_F32 && e.gamma != nullptr) {
+      // the lanes of a group hold the pieces of one token row; the warp's share of the row goes to the reduction buffer
+#pragma unroll
+      for (int d = 1; d < G::kLanes; d <<= 1) ss_part += __shfl_xor_sync(0xffffffffu, ss_part, d);
+      if (sub == 0) ss_red[row0 + p * G::kRows] = live ? ss_part : 0.f;
     }
     if (EPI == kEpiSliceMax) {
       // the lanes of a group hold the pieces of one token row
 #pragma unroll
       for (int d = 1; d < G::kLanes; d <<= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, d));
       if (live && sub == 0) e.part_val[(int64_t)(n_warp0 >> 5) * e.part_ld + tok] = smax;
+    }
+  }
+  if (kRes && !OUT_F32 && e.gamma != nullptr) {
+    // one sum of squares per token and CTA (128 features): the four warps' shares are added in a fixed order by
+    // warp q for tokens 8q .. 8q+7 of the block (ss_red_block: [4 warps][32 tokens], double-buffered by the caller)
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const int q = (n_warp0 >> 5) & 3;
+    if (lane < 8) {
+      const int tl = q * 8 + lane, tok = tok0 + tl;
+      if (tok < tok_limit)
+        e.ss_out[(int64_t)tok * e.ss_out_ld + (n_warp0 >> 7)] =
+            ((ss_red_block[tl] + ss_red_block[32 + tl]) + ss_red_block[64 + tl]) + ss_red_block[96 + tl];
     }
   }
 }
@@ -508,7 +569,7 @@ __device__ __forceinline__ float4 ldg_f4(const float* p) {
 // requested a block ahead: with global loads in flight, the waits for the shared-memory words of the
 // transposition waited for them too.
 constexpr int kRopeMetaBytes = 2 * kMaxChunk * 4;
-constexpr int kEpiStageBytes = 4 * 128 * 16;  // the larger of the two uses of the epilogue staging area
+constexpr int kEpiStageBytes = 4 * 128 * 16 + 1024;  // residual pieces (8 KB, or the rotary inputs) + the norm's reduction buffer
 static_assert(kEpiStageBytes >= kRopeMetaBytes, "staging area");
 __device__ __forceinline__ void rope_meta_stage(const EpiArgs& e, int* s_pos, int* s_dst, int tok_base, int tok_limit, int et,
                                                 bool is_q, bool is_v) {
@@ -526,6 +587,30 @@ __device__ __forceinline__ void rope_meta_stage(const EpiArgs& e, int* s_pos, in
   }
 }
 
+// Consumer side of the folded RMS norm: the row scales of the tile's tokens, formed once per tile by the four
+// epilogue warps (token per thread, the slices of a token added in ascending order) while the main loop runs.
+__device__ __forceinline__ void norm_scale_stage(const EpiArgs& e, float* s_scale, int tok_base, int tok_limit, int et) {
+#pragma unroll
+  for (int t = et; t < kMaxChunk; t += 128) {
+    const int tok = tok_base + t;
+    if (tok < tok_limit) {
+      // a token's slices lie side by side (16-byte aligned rows): few, wide, independent loads
+      const float4* src = reinterpret_cast<const float4*>(e.ss_in + (int64_t)tok * e.ss_in_ld);
+      float sum = 0.f;
+#pragma unroll 8
+      for (int q4 = 0; q4 < (e.ss_slices >> 2); ++q4) {
+        const float4 f = src[q4];
+        sum += f.x;
+        sum += f.y;
+        sum += f.z;
+        sum += f.w;
+      }
+      for (int sl = e.ss_slices & ~3; sl < e.ss_slices; ++sl) sum += e.ss_in[(int64_t)tok * e.ss_in_ld + sl];
+      s_scale[t] = 1.0f / sqrtf(sum / e.norm_dim + e.norm_eps);
+    }
+  }
+}
+
 // Epilogue block of the QKV projection with fused rotary embedding (head_dim 128 = one CTA's 128
 // weight rows = one head).  v: this lane's feature d = 32*quarter + lane for the block's 32 tokens.
 // The rotation pairs feature d with d +- 64, which lives in the warp two quarters away, so the four
@@ -534,7 +619,8 @@ __device__ __forceinline__ void rope_meta_stage(const EpiArgs& e, int* s_pos, in
 // equals projection -> rope bit for bit.  After the exchange four lanes share a token row (8 features
 // each), so the cos/sin reads and the stores of an instruction cover 8 rows, not 32.
 __device__ __forceinline__ void epilogue_rope_block(const float* v, const EpiArgs& e, float* scr_all, int quarter, int lane,
-                                                    int head, int tok0, int tok_limit, const int* s_pos, const int* s_dst) {
+                                                    int head, int tok0, int tok_limit, const int* s_pos, const int* s_dst,
+                                                    const float* s_scale) {
   float* scr = scr_all + quarter * 32 * kScrLd;
   const bool is_v = head >= e.nh + e.nkv;
   const int sub = lane & 3, row0 = lane >> 2;
@@ -554,8 +640,15 @@ __device__ __forceinline__ void epilogue_rope_block(const float* v, const EpiArg
       }
     }
   }
+  if (s_scale != nullptr) {
+    // folded RMS norm: the projection of the normalised row is the projection of the row times its scale; scaled and
+    // rounded after the exchange, where a lane holds one token's values
 #pragma unroll
-  for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = __bfloat162float(__float2bfloat16_rn(v[i]));
+    for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = v[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) scr[i * kScrLd + lane] = __bfloat162float(__float2bfloat16_rn(v[i]));
+  }
   asm volatile("bar.sync 1, 128;" ::: "memory");
   float o[4][8];
 #pragma unroll
@@ -565,9 +658,20 @@ __device__ __forceinline__ void epilogue_rope_block(const float* v, const EpiArg
     const float4 a0 = *reinterpret_cast<const float4*>(own), a1 = *reinterpret_cast<const float4*>(own + 4);
     o[p][0] = a0.x, o[p][1] = a0.y, o[p][2] = a0.z, o[p][3] = a0.w;
     o[p][4] = a1.x, o[p][5] = a1.y, o[p][6] = a1.z, o[p][7] = a1.w;
+    const float sc = s_scale != nullptr ? s_scale[r] : 1.0f;
+    if (s_scale != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[p][j] = __bfloat162float(__float2bfloat16_rn(o[p][j] * sc));
+    }
     if (!is_v) {
       const float* oth = scr_all + (quarter ^ 2) * 32 * kScrLd + r * kScrLd + sub * 8;
-      const float4 b0 = *reinterpret_cast<const float4*>(oth), b1 = *reinterpret_cast<const float4*>(oth + 4);
+      float4 b0 = *reinterpret_cast<const float4*>(oth), b1 = *reinterpret_cast<const float4*>(oth + 4);
+      if (s_scale != nullptr) {
+        b0.x = __bfloat162float(__float2bfloat16_rn(b0.x * sc)), b0.y = __bfloat162float(__float2bfloat16_rn(b0.y * sc));
+        b0.z = __bfloat162float(__float2bfloat16_rn(b0.z * sc)), b0.w = __bfloat162float(__float2bfloat16_rn(b0.w * sc));
+        b1.x = __bfloat162float(__float2bfloat16_rn(b1.x * sc)), b1.y = __bfloat162float(__float2bfloat16_rn(b1.y * sc));
+        b1.z = __bfloat162float(__float2bfloat16_rn(b1.z * sc)), b1.w = __bfloat162float(__float2bfloat16_rn(b1.w * sc));
+      }
       if (tok0 + r < tok_limit) {
         const float4 c0 = cs[p][0], c1 = cs[p][1], s0 = cs[p][2], s1 = cs[p][3];
         // two rounded products and one rounded sum, as the separate rope kernel computes them
@@ -631,6 +735,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   int* s_pos = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);
   int* s_dst = s_pos + kMaxChunk;
   uint4* res_buf = reinterpret_cast<uint4*>(s_pos) + ((threadIdx.x >> 5) & 3) * 128;  // 2 KB per epilogue warp
+  float* s_scale = reinterpret_cast<float*>(s_dst + kMaxChunk);  // folded RMS norm, consumer side: see norm_scale_stage
+  float* ss_red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_pos) + 8192);  // producer side: 2 x [4][32] floats
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   rd::pdl_launch_dependents();  // the next kernel may set itself up while this one runs
@@ -770,11 +876,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr bool kBias = (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES);
       const float bias = (kBias && n_warp0 + lane < N) ? __bfloat162float(epi.bias[n_warp0 + lane]) : 0.f;
       const int rope_head = (n_warp0 - quarter * 32) / 128;
-      if (EPI == kEpiQkvRope) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the blocks of the tile before have read their entries
+      constexpr bool kNormIn = (EPI == kEpiQkvRope || EPI == RD_EPI_SWIGLU);
+      const bool norm_in = kNormIn && epi.ss_in != nullptr;
+      if (EPI == kEpiQkvRope || norm_in) asm volatile("bar.sync 1, 128;" ::: "memory");  // the tile before has read its entries
+      if (EPI == kEpiQkvRope)
         rope_meta_stage(epi, s_pos, s_dst, tok_base, tok_limit, (int)threadIdx.x - 64, rope_head < epi.nh,
                         rope_head >= epi.nh + epi.nkv);
-      }
+      if (norm_in) norm_scale_stage(epi, s_scale, tok_base, tok_limit, (int)threadIdx.x - 64);
+      // producer side of the folded RMS norm: this lane's eight gamma values (its features are the same in every block)
+      uint4 gamma8 = make_uint4(0u, 0u, 0u, 0u);
+      if (kRes && !OUT_F32 && epi.gamma != nullptr && vec_ok)
+        gamma8 = *reinterpret_cast<const uint4*>(epi.gamma + n_warp0 + (lane & 3) * 8);
       if (kRes && vec_ok) {
         if (OUT_F32)
           res_next.load(epi, tok_base, out0, tok_limit, lane);
@@ -786,7 +898,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc_fence_after();
-      if (EPI == kEpiQkvRope) asm volatile("bar.sync 1, 128;" ::: "memory");  // the staged entries are visible
+      if (EPI == kEpiQkvRope || norm_in) asm volatile("bar.sync 1, 128;" ::: "memory");  // the staged entries are visible
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
 #pragma unroll 1
       for (int c = 0; c < cols; c += 32) {
@@ -804,12 +916,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         if (EPI == kEpiQkvRope) {
-          epilogue_rope_block(v, epi, scratch, quarter, lane, rope_head, tok_base + c, tok_limit, s_pos + c, s_dst + c);
+          epilogue_rope_block(v, epi, scratch, quarter, lane, rope_head, tok_base + c, tok_limit, s_pos + c, s_dst + c,
+                              norm_in ? s_scale + c : nullptr);
         } else if (EPI == kEpiArgmax) {
           epilogue_argmax_block(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N);
         } else {
           epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok, bias);
-          epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
+          epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur,
+                                       norm_in ? s_scale + c : nullptr, gamma8, ss_red + ((c >> 5) & 1) * 128);
         }
       }
       tc_fence_before();
@@ -923,6 +1037,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   int* s_pos = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 256);
   int* s_dst = s_pos + kMaxChunk;
   uint4* res_buf = reinterpret_cast<uint4*>(s_pos) + ((threadIdx.x >> 5) & 3) * 128;  // 2 KB per epilogue warp
+  float* s_scale = reinterpret_cast<float*>(s_dst + kMaxChunk);  // folded RMS norm, consumer side: see norm_scale_stage
+  float* ss_red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_pos) + 8192);  // producer side: 2 x [4][32] floats
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
@@ -1082,11 +1198,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr bool kBias = (EPI == RD_EPI_BIAS || EPI == RD_EPI_BIAS_SILU || EPI == RD_EPI_BIAS_SILU_RES);
       const float bias = (kBias && n_warp0 + lane < N) ? __bfloat162float(epi.bias[n_warp0 + lane]) : 0.f;
       const int rope_head = (n_warp0 - quarter * 32) / 128;
-      if (EPI == kEpiQkvRope) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the blocks of the tile before have read their entries
+      constexpr bool kNormIn = (EPI == kEpiQkvRope || EPI == RD_EPI_SWIGLU);
+      const bool norm_in = kNormIn && epi.ss_in != nullptr;
+      if (EPI == kEpiQkvRope || norm_in) asm volatile("bar.sync 1, 128;" ::: "memory");  // the tile before has read its entries
+      if (EPI == kEpiQkvRope)
         rope_meta_stage(epi, s_pos, s_dst, tok_base, tok_limit, (int)threadIdx.x - 64, rope_head < epi.nh,
                         rope_head >= epi.nh + epi.nkv);
-      }
+      if (norm_in) norm_scale_stage(epi, s_scale, tok_base, tok_limit, (int)threadIdx.x - 64);
+      // producer side of the folded RMS norm: this lane's eight gamma values (its features are the same in every block)
+      uint4 gamma8 = make_uint4(0u, 0u, 0u, 0u);
+      if (kRes && !OUT_F32 && epi.gamma != nullptr && vec_ok)
+        gamma8 = *reinterpret_cast<const uint4*>(epi.gamma + n_warp0 + (lane & 3) * 8);
       if (kRes && vec_ok) {
         if (OUT_F32)
           res_next.load(epi, tok_base, out0, tok_limit, lane);
@@ -1098,7 +1220,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc_fence_after();
-      if (EPI == kEpiQkvRope) asm volatile("bar.sync 1, 128;" ::: "memory");  // the staged entries are visible
+      if (EPI == kEpiQkvRope || norm_in) asm volatile("bar.sync 1, 128;" ::: "memory");  // the staged entries are visible
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kMaxChunk;
 #pragma unroll 1
       for (int c = 0; c < cols; c += 32) {
@@ -1116,12 +1238,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
         if (EPI == kEpiQkvRope) {
-          epilogue_rope_block(v, epi, scratch, quarter, lane, rope_head, tok_base + c, tok_limit, s_pos + c, s_dst + c);
+          epilogue_rope_block(v, epi, scratch, quarter, lane, rope_head, tok_base + c, tok_limit, s_pos + c, s_dst + c,
+                              norm_in ? s_scale + c : nullptr);
         } else if (EPI == kEpiArgmax) {
           epilogue_argmax_block(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N);
         } else {
           epilogue_math<EPI>(v, epi, n_warp0 + lane, N, !vec_ok, bias);
-          epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur);
+          epilogue_block<EPI, OUT_F32>(v, epi, scr, lane, n_warp0, tok_base + c, tok_limit, N, vec_ok, res_cur,
+                                       norm_in ? s_scale + c : nullptr, gamma8, ss_red + ((c >> 5) & 1) * 128);
         }
       }
       tc_fence_before();
@@ -1333,10 +1457,55 @@ extern "C" int rd_gemm_bf16_tc(const void* plan, int out_dtype, void* C, int64_t
   return launch_epi(p, out_dtype, e, m_dev, epilogue, status, s);
 }
 
-extern "C" int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, void* q_out, void* k_cache, void* v_cache,
-                                        const int32_t* tok_row, const int32_t* tok_pos, const int32_t* tok_slot,
-                                        const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv, int hd,
-                                        int max_len, int32_t* status, void* stream) {
+static bool norm_in_ok(const GemmPlan* p, const float* ss_in, int64_t ss_ld, int ss_slices, int norm_dim, float eps) {
+  (void)p;
+  return ss_in && ((uintptr_t)ss_in & 15) == 0 && ss_slices >= 1 && ss_ld >= ss_slices && ss_ld % 4 == 0 && norm_dim >= 1 &&
+         eps >= 0.f;
+}
+
+extern "C" int rd_gemm_bf16_tc_res_norm(const void* plan, void* C, int64_t ldc, const void* R, int64_t ldr, const int32_t* m_dev,
+                                        const void* gamma, void* C2, int64_t ldc2, float* ss_out, int64_t ss_ld,
+                                        int32_t* status, void* stream) {
+  RD_REQUIRE(plan && C && R && gamma && C2 && ss_out, RD_ERR_ARG);
+  const GemmPlan* p = static_cast<const GemmPlan*>(plan);
+  RD_REQUIRE(p->N % 128 == 0 && ss_ld >= p->N / 128, RD_ERR_SIZE);
+  RD_REQUIRE((((uintptr_t)C | (uintptr_t)R | (uintptr_t)gamma | (uintptr_t)C2) & 15) == 0 && (ldc * 2) % 16 == 0 &&
+                 (ldr * 2) % 16 == 0 && (ldc2 * 2) % 16 == 0,
+             RD_ERR_ALIGN);
+  EpiArgs e{};
+  e.C = C;
+  e.ldc = ldc;
+  e.R = R;
+  e.ldr = ldr;
+  e.gamma = (const __nv_bfloat16*)gamma;
+  e.C2 = (__nv_bfloat16*)C2;
+  e.ldc2 = ldc2;
+  e.ss_out = ss_out;
+  e.ss_out_ld = ss_ld;
+  return launch_epi(p, RD_BF16, e, m_dev, RD_EPI_RES, status, (cudaStream_t)stream);
+}
+
+extern "C" int rd_gemm_bf16_tc_swiglu_normed(const void* plan, void* C, int64_t ldc, const int32_t* m_dev, const float* ss_in,
+                                             int64_t ss_ld, int ss_slices, int norm_dim, float eps, int32_t* status,
+                                             void* stream) {
+  RD_REQUIRE(plan && C, RD_ERR_ARG);
+  const GemmPlan* p = static_cast<const GemmPlan*>(plan);
+  RD_REQUIRE(p->N % 2 == 0 && norm_in_ok(p, ss_in, ss_ld, ss_slices, norm_dim, eps), RD_ERR_SIZE);
+  EpiArgs e{};
+  e.C = C;
+  e.ldc = ldc;
+  e.ss_in = ss_in;
+  e.ss_in_ld = ss_ld;
+  e.ss_slices = ss_slices;
+  e.norm_dim = (float)norm_dim;
+  e.norm_eps = eps;
+  return launch_epi(p, RD_BF16, e, m_dev, RD_EPI_SWIGLU, status, (cudaStream_t)stream);
+}
+
+static int qkv_rope_launch(const void* plan, const int32_t* m_dev, void* q_out, void* k_cache, void* v_cache,
+                           const int32_t* tok_row, const int32_t* tok_pos, const int32_t* tok_slot, const float* cos_table,
+                           const float* sin_table, int n_pos, int nh, int nkv, int hd, int max_len, const float* ss_in,
+                           int64_t ss_ld, int ss_slices, int norm_dim, float eps, int32_t* status, void* stream) {
   RD_REQUIRE(plan && q_out && k_cache && v_cache && tok_row && tok_pos && tok_slot && cos_table && sin_table, RD_ERR_ARG);
   const GemmPlan* p = static_cast<const GemmPlan*>(plan);
   RD_REQUIRE(hd == 128 && nh >= 1 && nkv >= 1 && n_pos >= 1 && max_len >= 1, RD_ERR_SIZE);
@@ -1358,7 +1527,33 @@ extern "C" int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, 
   e.nh = nh;
   e.nkv = nkv;
   e.max_len = max_len;
+  if (ss_in) {
+    RD_REQUIRE(norm_in_ok(p, ss_in, ss_ld, ss_slices, norm_dim, eps), RD_ERR_SIZE);
+    e.ss_in = ss_in;
+    e.ss_in_ld = ss_ld;
+    e.ss_slices = ss_slices;
+    e.norm_dim = (float)norm_dim;
+    e.norm_eps = eps;
+  }
   return launch_epi(p, RD_BF16, e, m_dev, kEpiQkvRope, status, (cudaStream_t)stream);
+}
+
+extern "C" int rd_gemm_bf16_tc_qkv_rope(const void* plan, const int32_t* m_dev, void* q_out, void* k_cache, void* v_cache,
+                                        const int32_t* tok_row, const int32_t* tok_pos, const int32_t* tok_slot,
+                                        const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv, int hd,
+                                        int max_len, int32_t* status, void* stream) {
+  return qkv_rope_launch(plan, m_dev, q_out, k_cache, v_cache, tok_row, tok_pos, tok_slot, cos_table, sin_table, n_pos, nh, nkv,
+                         hd, max_len, nullptr, 0, 0, 0, 0.f, status, stream);
+}
+
+extern "C" int rd_gemm_bf16_tc_qkv_rope_normed(const void* plan, const int32_t* m_dev, void* q_out, void* k_cache, void* v_cache,
+                                               const int32_t* tok_row, const int32_t* tok_pos, const int32_t* tok_slot,
+                                               const float* cos_table, const float* sin_table, int n_pos, int nh, int nkv,
+                                               int hd, int max_len, const float* ss_in, int64_t ss_ld, int ss_slices,
+                                               int norm_dim, float eps, int32_t* status, void* stream) {
+  RD_REQUIRE(ss_in, RD_ERR_ARG);
+  return qkv_rope_launch(plan, m_dev, q_out, k_cache, v_cache, tok_row, tok_pos, tok_slot, cos_table, sin_table, n_pos, nh, nkv,
+                         hd, max_len, ss_in, ss_ld, ss_slices, norm_dim, eps, status, stream);
 }
 
 static inline int64_t part_ld_of(int m_max) { return ((int64_t)m_max + 31) / 32 * 32; }

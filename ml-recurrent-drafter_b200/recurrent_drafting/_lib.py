@@ -39,6 +39,10 @@ SIGNATURES = {
     "rd_gemm_plan_destroy": (None, [_P]),
     "rd_gemm_bf16_tc": (_I, [_P, _I, _P, _L, _P, _P, _L, _P, _I, _P, _P]),
     "rd_gemm_bf16_tc_qkv_rope": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]),
+    "rd_gemm_bf16_tc_res_norm": (_I, [_P, _P, _L, _P, _L, _P, _P, _P, _L, _P, _L, _P, _P]),
+    "rd_gemm_bf16_tc_swiglu_normed": (_I, [_P, _P, _L, _P, _P, _L, _I, _I, _F, _P, _P]),
+    "rd_gemm_bf16_tc_qkv_rope_normed": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _I, _F,
+                                              _P, _P]),
     "rd_gemm_argmax_workspace_bytes": (_L, [_I, _I]),
     "rd_gemm_bf16_tc_argmax": (_I, [_P, _P, _P, _L, _P, _P, _P, _P]),
     "rd_gemm_bf16_tc_slicemax": (_I, [_P, _I, _P, _L, _P, _P, _L, _P, _P]),

@@ -71,15 +71,44 @@ class _Linear:
 
     def qkv_rope(self, a: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_row, tok_pos,
                  tok_slot, cos: torch.Tensor, sin: torch.Tensor, nh: int, nkv: int, hd: int, m_dev, m_max: int,
-                 status: Optional[torch.Tensor]) -> None:
+                 status: Optional[torch.Tensor], norm=None) -> None:
         """This weight as the packed QKV projection with rotary embedding and cache append in the
         GEMM epilogue (rd_gemm_bf16_tc_qkv_rope); tensor-core path only."""
         if not self._tc_ok(a, a.stride(0)):
             raise _lib.RedrafterError("the fused QKV projection needs the tensor-core GEMM path (bf16, aligned operands)")
         plan = self._plan(a, a.stride(0), m_max)
+        if norm is not None:
+            # `a` holds gamma-scaled, not normalised rows: the 1 / rms of each row is applied in the epilogue
+            ss, dim, eps = norm
+            _lib.call("rd_gemm_bf16_tc_qkv_rope_normed", plan, _lib.ptr(m_dev), _lib.ptr(q_out), _lib.ptr(k_cache),
+                      _lib.ptr(v_cache), _lib.ptr(tok_row), _lib.ptr(tok_pos), _lib.ptr(tok_slot), _lib.ptr(cos), _lib.ptr(sin),
+                      cos.shape[0], nh, nkv, hd, k_cache.shape[2], _lib.ptr(ss), ss.stride(0), dim // 128, dim, eps,
+                      _lib.ptr(status), _lib.stream())
+            return
         _lib.call("rd_gemm_bf16_tc_qkv_rope", plan, _lib.ptr(m_dev), _lib.ptr(q_out), _lib.ptr(k_cache), _lib.ptr(v_cache),
                   _lib.ptr(tok_row), _lib.ptr(tok_pos), _lib.ptr(tok_slot), _lib.ptr(cos), _lib.ptr(sin), cos.shape[0], nh, nkv,
                   hd, k_cache.shape[2], _lib.ptr(status), _lib.stream())
+
+    def residual_with_norm(self, a: torch.Tensor, c: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor,
+                           c2: torch.Tensor, ss: torch.Tensor, m_dev, m_max: int, status: Optional[torch.Tensor]) -> None:
+        """c = a @ weight^T + residual, and the producer half of the RMS norm that follows: c2 = c * gamma and the
+        per-slice sums of squares ss [m_max, >= features / 128] (rd_gemm_bf16_tc_res_norm); tensor-core path only."""
+        if not self._tc_ok(a, a.stride(0)):
+            raise _lib.RedrafterError("the folded RMS norm needs the tensor-core GEMM path (bf16, aligned operands)")
+        plan = self._plan(a, a.stride(0), m_max)
+        _lib.call("rd_gemm_bf16_tc_res_norm", plan, _lib.ptr(c), c.stride(0), _lib.ptr(residual), residual.stride(0),
+                  _lib.ptr(m_dev), _lib.ptr(gamma), _lib.ptr(c2), c2.stride(0), _lib.ptr(ss), ss.stride(0), _lib.ptr(status),
+                  _lib.stream())
+
+    def swiglu_normed(self, a: torch.Tensor, c: torch.Tensor, ss: torch.Tensor, dim: int, eps: float, m_dev, m_max: int,
+                      status: Optional[torch.Tensor]) -> None:
+        """SwiGLU projection of rows that are gamma-scaled but not normalised: each row's 1 / rms, from the sums of
+        squares ss, is applied in the epilogue (rd_gemm_bf16_tc_swiglu_normed); tensor-core path only."""
+        if not self._tc_ok(a, a.stride(0)):
+            raise _lib.RedrafterError("the folded RMS norm needs the tensor-core GEMM path (bf16, aligned operands)")
+        plan = self._plan(a, a.stride(0), m_max)
+        _lib.call("rd_gemm_bf16_tc_swiglu_normed", plan, _lib.ptr(c), c.stride(0), _lib.ptr(m_dev), _lib.ptr(ss), ss.stride(0),
+                  dim // 128, dim, eps, _lib.ptr(status), _lib.stream())
 
     def argmax(self, a: torch.Tensor, out32: torch.Tensor, workspace: torch.Tensor, m_dev, m_max: int,
                status: Optional[torch.Tensor]) -> None:
@@ -387,6 +416,8 @@ class LlamaForCausalLM(nn.Module):
             for name, width in (("h", H), ("xn", H), ("qkv", (nh + 2 * nkv) * hd), ("q", nh * hd), ("attn", nh * hd),
                                 ("act", self.config.intermediate_size), ("hidden", H)):
                 full[name] = torch.empty(cap_m, width, dtype=dt, device=dev)
+            # folded RMS norm: per-token sums of squares by 128-feature slice
+            full["ss"] = torch.empty(cap_m, ((H + 127) // 128 + 3) // 4 * 4, dtype=torch.float32, device=dev)
         if logit_rows > cap_l:
             cap_l = logit_rows
             full["logits"] = torch.empty(cap_l, self.config.vocab_size, dtype=torch.float32, device=dev)
@@ -428,13 +459,21 @@ class LlamaForCausalLM(nn.Module):
         dld_b = dense_mask.stride(0) if dense_mask is not None else 0
         fused_rope = (self.dtype == torch.bfloat16 and hd == 128 and H % 64 == 0 and xn.data_ptr() % 16 == 0
                       and os.environ.get("RD_FUSED_ROPE", "1") != "0")
+        # RMS norms between the projections folded into them (RD_FUSED_NORM=1): o_proj / down_proj also write the
+        # gamma-scaled row and its sums of squares, gate/up and the next layer's QKV apply 1 / rms in their epilogues;
+        # the first layer's input norm and the final norm keep their own kernel.  Off unless asked for: it removes 63
+        # launches of a 7B step, but the longer epilogues cost as much as the launches did.
+        fused_norm = (fused_rope and H % 128 == 0 and h.data_ptr() % 16 == 0
+                      and os.environ.get("RD_FUSED_NORM", "0") == "1")
+        ss = ws["ss"] if fused_norm else None
         for l in range(self.n_layers):
-            _lib.call("rd_rmsnorm", code, _lib.ptr(h), _lib.ptr(self.ln1[l]), _lib.ptr(xn), m_max, md, H, self.eps, st)
+            if not fused_norm or l == 0:
+                _lib.call("rd_rmsnorm", code, _lib.ptr(h), _lib.ptr(self.ln1[l]), _lib.ptr(xn), m_max, md, H, self.eps, st)
             kc, vc = cache_tensor[l, 0], cache_tensor[l, 1]
             if fused_rope:
                 # rotary embedding and the cache append ride on the projection's epilogue
                 lin["qkv"][l].qkv_rope(xn, q, kc, vc, tok_row, tok_pos, tok_slot, cos, sin, nh, nkv, hd, m_dev, m_max,
-                                       self.gemm_status)
+                                       self.gemm_status, norm=(ss, H, self.eps) if fused_norm and l > 0 else None)
             else:
                 lin["qkv"][l](xn, qkv, _lib.EPI_NONE, m_dev=m_dev, m_max=m_max, status=self.gemm_status)
                 _lib.call("rd_rope_kv_write", code, _lib.ptr(qkv), _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(tok_row),
@@ -442,6 +481,14 @@ class LlamaForCausalLM(nn.Module):
                           hd, max_len, st)
             self._attention(code, q, kc, vc, attn, row_start, kv_begin, base_len, batch, m_max, max_new, max_kv, mode, tree_mask,
                             mask_words, dense_mask, dld_q, dld_b, st)
+            if fused_norm:
+                lin["o"][l].residual_with_norm(attn, h, h, self.ln2[l], xn, ss, m_dev, m_max, self.gemm_status)
+                lin["gu"][l].swiglu_normed(xn, act, ss, H, self.eps, m_dev, m_max, self.gemm_status)
+                if l + 1 < self.n_layers:
+                    lin["down"][l].residual_with_norm(act, h, h, self.ln1[l + 1], xn, ss, m_dev, m_max, self.gemm_status)
+                else:
+                    lin["down"][l](act, h, _lib.EPI_RES, residual=h, m_dev=m_dev, m_max=m_max, status=self.gemm_status)
+                continue
             lin["o"][l](attn, h, _lib.EPI_RES, residual=h, m_dev=m_dev, m_max=m_max, status=self.gemm_status)
             _lib.call("rd_rmsnorm", code, _lib.ptr(h), _lib.ptr(self.ln2[l]), _lib.ptr(xn), m_max, md, H, self.eps, st)
             lin["gu"][l](xn, act, _lib.EPI_SWIGLU, m_dev=m_dev, m_max=m_max, status=self.gemm_status)

@@ -250,3 +250,53 @@ def test_slice_maxima_and_sliced_topk_equal_the_plain_path(out_dtype, M, N, K, l
         torch.cuda.synchronize()
         for x, y in ((p0.val, p1.val), (p0.idx, p1.idx), (p0.cnt, p1.cnt), (p0.masked, p1.masked)):
             assert torch.equal(x[:n_live], y[:n_live])
+
+
+@pytest.mark.parametrize("M,live,H,K1,N2", [(900, 777, 512, 256, 1024), (300, 300, 4096, 128, 512), (64, 5, 256, 64, 256)])
+def test_gemm_tc_folded_rms_norm(M, live, H, K1, N2):
+    """The residual projection also emits the gamma-scaled rows and their sums of squares per 128-feature slice
+    (rd_gemm_bf16_tc_res_norm); the next projection scales its accumulator rows by 1 / rms
+    (rd_gemm_bf16_tc_swiglu_normed).  Together they must equal residual add -> LlamaRMSNorm -> SwiGLU projection on
+    the same rounded values, and give the same bits from launch to launch (no atomics in the statistics)."""
+    from recurrent_drafting import _lib
+    from recurrent_drafting.modeling_llama import _Linear
+
+    g = torch.Generator(device="cuda").manual_seed(11 + M)
+    eps = 1e-6
+    a = (torch.randn(M, K1, generator=g, device="cuda") * 0.5).bfloat16()
+    w1 = (torch.randn(H, K1, generator=g, device="cuda") * 0.1).bfloat16()
+    w2 = (torch.randn(N2, H, generator=g, device="cuda") * 0.1).bfloat16()
+    gamma = (1.0 + 0.2 * torch.randn(H, generator=g, device="cuda")).bfloat16()
+    h0 = torch.randn(M, H, generator=g, device="cuda").bfloat16()
+    m_dev = torch.tensor([live], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    l1, l2 = _Linear(w1), _Linear(w2)
+    runs = []
+    for _ in range(2):
+        h = h0.clone()
+        x2 = torch.full((M, H), 3.0, dtype=torch.bfloat16, device="cuda")
+        ss = torch.full((M, (H // 128 + 3) // 4 * 4 + 4), -1.0, dtype=torch.float32, device="cuda")
+        out = torch.full((M, N2 // 2), 7.0, dtype=torch.bfloat16, device="cuda")
+        l1.residual_with_norm(a, h, h, gamma, x2, ss, m_dev, M, status)
+        l2.swiglu_normed(x2, out, ss, H, eps, m_dev, M, status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        runs.append((h, x2, ss, out))
+    h, x2, ss, out = runs[0]
+    for x, y in zip(runs[0], runs[1]):
+        assert torch.equal(x, y)
+    h_ref = (a.float() @ w1.float().T + h0.float()).bfloat16()
+    torch.testing.assert_close(h[:live].float(), h_ref[:live].float(), rtol=2e-2, atol=2e-2)
+    hr = h[:live].float()  # the statistics are defined on the rounded residual stream the kernel wrote
+    want_ss = (hr * hr).reshape(live, H // 128, 128).sum(-1)
+    torch.testing.assert_close(ss[:live, : H // 128], want_ss, rtol=1e-5, atol=1e-5)
+    assert torch.all(ss[live:] == -1.0) and torch.all(ss[:, H // 128:] == -1.0)
+    assert torch.equal(x2[:live], (hr * gamma.float()).bfloat16())
+    r = torch.rsqrt((hr * hr).mean(-1, keepdim=True) + eps)
+    normed = gamma.float() * (hr * r).bfloat16().float()  # LlamaRMSNorm: weight * x_normalised.to(dtype)
+    acc = normed.bfloat16().float() @ w2.float().T
+    want = torch.nn.functional.silu(acc[:, 0::2]) * acc[:, 1::2]
+    scale = want.abs().max().item()
+    err = (out[:live].float() - want).abs().max().item()
+    assert err <= 2e-2 * scale, (err, scale)
+    assert torch.all(out[live:] == 7.0) and torch.all(x2[live:] == 3.0)

@@ -20,3 +20,14 @@ def test_bf16_head_dim_128_decode_steps_against_oracle(batch, width, length, ste
     # random-init logits are closely spaced (the best and second-best differ by less than the bf16 error
     # on some rows), so some arg-max flips against the fp32 oracle are expected; most rows must agree
     assert r["argmax_agree"] >= 0.8, r
+
+
+def test_bf16_head_dim_128_decode_steps_with_folded_norms(monkeypatch):
+    """The same check with the RMS norms inside the stack folded into the projections around them
+    (RD_FUSED_NORM=1): same tolerances against the oracle."""
+    monkeypatch.setenv("RD_FUSED_NORM", "1")
+    r = hd128_step_check(batch=8, width=45, length=5, steps=2)
+    assert r["steps"] == 2
+    assert r["logit_err"] <= 2e-2 * r["logit_scale"], r
+    assert r["ctx_err"] <= 3e-2, r
+    assert r["argmax_agree"] >= 0.8, r

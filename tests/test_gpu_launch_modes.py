@@ -35,7 +35,7 @@ def _child() -> None:
 
 def _run(env_extra):
     env = dict(os.environ)
-    for k in ("RD_PDL", "RD_FUSED_ROPE", "RD_GEMM_PAIRS", "RD_FUSED_HEAD", "RD_CUDA_GRAPHS"):
+    for k in ("RD_PDL", "RD_FUSED_ROPE", "RD_GEMM_PAIRS", "RD_FUSED_HEAD", "RD_CUDA_GRAPHS", "RD_FUSED_NORM"):
         env.pop(k, None)
     env.update(env_extra)
     r = subprocess.run([sys.executable, os.path.abspath(__file__)], env=env, capture_output=True, text=True, timeout=600)
@@ -51,6 +51,13 @@ def test_launch_and_fusion_switches_do_not_change_the_tokens():
     for setting in ({"RD_PDL": "0"}, {"RD_FUSED_ROPE": "0"}, {"RD_GEMM_PAIRS": "0"}, {"RD_FUSED_HEAD": "0"},
                     {"RD_CUDA_GRAPHS": "0"}):
         assert _run(setting) == base, setting
+    # the folded RMS norms (RD_FUSED_NORM=1) round differently (once instead of twice before the projection), so they
+    # are compared among themselves: how the kernels are launched must not matter
+    on = {"RD_FUSED_NORM": "1"}
+    folded = _run(on)
+    assert len(folded) == 3 and all(len(row) == 96 for row in folded)
+    for setting in ({"RD_GEMM_PAIRS": "0"}, {"RD_CUDA_GRAPHS": "0"}):
+        assert _run(dict(on, **setting)) == folded, setting
 
 
 if __name__ == "__main__":

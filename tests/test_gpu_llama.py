@@ -205,3 +205,38 @@ def test_attention_tcgen05(mode, W, L, bases):
         mask[0, :, base[b] :] = np.tril(np.ones((n, n), dtype=bool)) if mode == "causal" else tree[b, :n, :n]
         want = ollama.attention(q[s : s + n].transpose(1, 0, 2)[None], ks, vs, mask)[0].transpose(1, 0, 2)
         np.testing.assert_allclose(got[s : s + n], want, rtol=2e-2, atol=2e-2)
+
+
+def test_forward_bf16_folded_norms_match_oracle_and_separate_kernels(monkeypatch):
+    """head_dim 128 with hidden and MLP sizes that are multiples of 64: the bf16 forward applies the
+    rotary embedding in the QKV epilogue and, when asked to (RD_FUSED_NORM=1), folds the norms inside the
+    stack into the GEMMs around them.  Its logits must stay within the bf16 tolerance of the fp32 oracle on the same rounded
+    weights and close to the forward that runs norms and rope as separate kernels."""
+    import recurrent_drafting as rd
+    from gpu_helpers import llama_config
+
+    cfg = dict(mb.C1_LLAMA, num_attention_heads=2, num_key_value_heads=2, intermediate_size=704, num_hidden_layers=3)
+    lw = mb.llama_weights(cfg, 77)
+    ids_np = mb.prompts(2, 24, 1000, 5)
+    ids = t(ids_np)
+    pos = torch.arange(24, device="cuda")[None, :].expand(2, 24)
+    outs = {}
+    for tag, env in (("folded", {"RD_FUSED_NORM": "1"}), ("separate", {"RD_FUSED_ROPE": "0"}), ("rope_only", {})):
+        for k in ("RD_FUSED_NORM", "RD_FUSED_ROPE"):
+            monkeypatch.delenv(k, raising=False)
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        llm = rd.modeling_llama.LlamaForCausalLM(llama_config(cfg)).to(device="cuda", dtype=torch.bfloat16)
+        llm.load_state_dict({k: torch.from_numpy(v) for k, v in lw.items()})
+        cache = rd.kv_cache.Cache(2, 64, 3, 2, 128, torch.bfloat16, torch.device("cuda"))
+        mask = rd.attention.causal_mask(ids != 0, 24, ids.device)
+        outs[tag] = llm(ids, attention_mask=mask, position_ids=pos, past_key_values=cache.sliced).logits.float().cpu().numpy()
+    oc = okv.Cache(2, 64, 3, 2, 128)
+    want, _ = ollama.forward(bf16_round(lw), cfg, ids_np, ota.padded_causal_mask(ids_np != 0, 24), pos.cpu().numpy(), oc.sliced)
+    scale = np.abs(want).max()
+    for tag, got in outs.items():
+        err = np.abs(got - want).max()
+        assert err <= 2e-2 * scale, (tag, err, scale)
+    assert np.array_equal(outs["rope_only"], outs["separate"]), "the fused rope epilogue must not change a bit"
+    assert np.abs(outs["folded"] - outs["separate"]).max() <= 2e-2 * scale
+    assert not np.array_equal(outs["folded"], outs["separate"]), "the folded-norm path did not run"
