@@ -374,6 +374,10 @@ def run_ours(args):
 
     model._comprehend_prompt = timed_prefill
     sink = torch.empty(B, max_length + 1, dtype=torch.int64).pin_memory()
+    # one short untimed request first: the timed one then measures a server in steady state (allocator blocks, pinned
+    # staging and descriptor sets of this call path exist), as the warm-up steps do for the device-resident figure
+    replicas.generate_sharded(model, prompts_all, max_length, shape, sargs, special, device=dev, max_steps=4, host_sink=sink)
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     res = replicas.generate_sharded(model, prompts_all, max_length, shape, sargs, special, device=dev, max_steps=K, host_sink=sink)
