@@ -166,9 +166,9 @@ __device__ __forceinline__ uint32_t umma_instr_desc(int n) {
 // The fewest chunks that respect the 256-token MMA limit are used unless that leaves compute units
 // (CTAs or CTA pairs) idle: a GEMM with few weight tiles (N = 4096) then cuts the tokens finer so
 // that about one tile exists per unit.  Finer chunks than that cost more than they balance: every
-// chunk re-reads its weight tile from L2, and the kernel is sensitive to that operand traffic (gate/up
-// at 761 tokens: 115 us with 3 chunks of 256 in 3.5 rounds of tiles, 135 us with 4 of 192, 150 us with
-// 6 of 128, although both leave fewer idle tile slots).
+// chunk is one more pass over its weight tile, with a tile's fixed costs (gate/up at 761 tokens: 115 us
+// with 3 chunks of 256 in 3.5 rounds of tiles, 135 us with 4 of 192, 150 us with 6 of 128, although both
+// leave fewer idle tile slots).
 struct Chunking {
   int n_chunks, chunk;
 };
@@ -1114,8 +1114,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int sb = 0; sb < n_sub; ++sb) {
             tma_load_2d_pair(sW + stage * L::kStageW + sb * L::kBoxW, &map_w, leader_full, (kb + sb) * BK, w_row0);
             // one box of just the rows the chunk's half fills (rounded up to 32): a chunk of 192 tokens moves 96
-            // rows per CTA, not 128, and the main loop is bound by these bytes.  (Several 32-row boxes instead of
-            // one tall one made the loop 25 % slower: the cost is per box as well as per byte.)
+            // rows per CTA, not 128 (1-2 % on the projections with four chunks).  Several 32-row boxes instead of
+            // one tall one made the loop 25 % slower: the cost of a load is per box far more than per byte.
             tma_load_2d_pair(sA + stage * L::kStageA + sb * L::kBoxA, map_a, leader_full, (kb + sb) * BK, tok0);
           }
           if (++stage == kStages) {
