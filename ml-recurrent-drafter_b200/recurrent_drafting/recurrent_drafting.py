@@ -113,8 +113,8 @@ class _StepGraphs:
         before = _lib.launches
         # Captured with capture_begin / capture_end rather than the torch.cuda.graph context manager: that one
         # synchronises the device and empties the allocator's caches (device and pinned host) before every capture,
-        # which cost a request between 0.07 and 0.6 s; the phases allocate nothing, so there is nothing to make room
-        # for.  Thread-local capture mode: other threads of the process (a server's other requests) may keep calling
+        # after which the request's next allocations go back to cudaMalloc; the phases allocate nothing, so there is
+        # nothing to make room for.  Three captures take 4-25 ms this way.  Thread-local capture mode: other threads of the process (a server's other requests) may keep calling
         # CUDA.
         def captured(graph, fn):
             graph.capture_begin(capture_error_mode="thread_local")
